@@ -5,6 +5,7 @@ from __future__ import annotations
 
 from ..parts.registry import register_architecture
 from ..parts.spec import BlockSpec, ModelSpec, PartSpec, RunStep
+from .bivizen_config import BivizenConfig
 from .model_config import Qwen2Config
 
 
@@ -46,3 +47,45 @@ def qwen2_spec(config: Qwen2Config) -> ModelSpec:
 
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config, qwen2_spec)
+
+
+def bivizen_spec(config: BivizenConfig) -> ModelSpec:
+    """Bivizen: every layer is a parallel block (one RMSNorm whose rows the mixer and the feed-forward both read,
+    their outputs added to the stream together, each times a learned scale per column) whose mixer is softmax
+    attention with its options, the gated delta rule or gated linear attention, as config.json lists them, and whose
+    feed-forward is a gated one with limits.  Tensors: embed, l<i>.norm1, l<i>.mix.*, l<i>.mlp.*, l<i>.ls1, l<i>.ls2,
+    final.norm, head."""
+    e = config.width
+    norm = PartSpec("rms", {"size": e, "eps": config.eps, "tensor": ""})
+    layers, first_v_mix = [], True
+    for i, l in enumerate(config.layers):
+        if l.type == "attention":
+            position = (PartSpec("rope_half_live", {"rotary_dim": l.rot_dims, "theta": l.rot_base}) if l.rot_dims
+                        else PartSpec("none"))
+            v_mix = None
+            if l.v_mix:
+                v_mix, first_v_mix = ("first" if first_v_mix else "mix"), False
+            mixer = PartSpec("capped_attention", {
+                "hidden": e, "heads": l.heads, "kv_heads": l.kv_heads, "head_dim": l.dim, "v_dim": l.vdim,
+                "scale": l.scale, "softcap": l.softcap, "window": None, "qkv_bias": True, "head_gate": True,
+                "v_mix": v_mix, "position": position})
+        elif l.type == "delta":
+            mixer = PartSpec("gated_delta", {"hidden": e, "heads": l.heads, "kv_heads": l.kv_heads, "head_dim": l.dim,
+                                             "v_dim": l.vdim, "conv": l.conv, "eps": config.eps})
+        else:
+            mixer = PartSpec("gla", {"hidden": e, "heads": l.heads, "head_dim": l.dim, "v_dim": l.vdim, "tau": l.tau,
+                                     "rank": l.rank, "eps": config.eps})
+        parts = {"norm": norm, "mixer": mixer}
+        names = {"norm": "norm1", "mixer": "mix.", "mixer_scale": "ls1"}
+        if l.mlp is not None:
+            parts["feed_forward"] = PartSpec("clamped_glu", {"hidden": e, "intermediate": l.mlp.ff,
+                                                             "limit": l.mlp.limit, "alpha": 1.702})
+            names.update(feed_forward="mlp.", feed_forward_scale="ls2")
+        layers.append(BlockSpec(kind="parallel", prefix=f"l{i}.", parts=parts, names=names))
+    return ModelSpec(
+        architecture=config.architecture, hidden_size=e, vocab_size=config.vocab, max_positions=config.max_positions,
+        layers=tuple(layers), order=tuple(RunStep(i) for i in range(len(layers))), final_norm=norm,
+        embedding_name="embed", final_norm_prefix="final.norm", output_name="head", eos_token_id=config.eos_token_id)
+
+
+register_architecture("Bivizen", BivizenConfig, bivizen_spec)

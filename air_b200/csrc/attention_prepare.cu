@@ -1,0 +1,99 @@
+// What stands between the fused projection of an attention layer and its attention kernel, for layers whose
+// keys and values differ in size or that want more than a bias and a rotation:
+//
+//   proj [T, ld] float32 holds, per token, q (H heads of dk), k (G heads of dk), v (G heads of dv) and, where the
+//   layer gates its heads, H gate logits, in this order.  Per token: add the bias; rotate the first `rot` elements
+//   of every head of q and k (element i with i + rot/2, angle position * inv_freq[i], evaluated here in 32-bit);
+//   mix the values with those of an earlier layer, v = (1 - lambda) v + lambda v_first (v_mode 2), or hand them on
+//   as v_first (v_mode 1); write q to q_out [T, H, dk], k and v into the token's place in the pages, and
+//   sigmoid(gate logits) to gate_out [T, H].
+//
+// A page holds the keys [G, P, dk] and behind them the values [G, P, dv]; with dk == dv that is [2, G, P, d], the
+// layout of the other attention kernels.
+#include "common.cuh"
+
+namespace air {
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+qkv_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias,
+                   const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
+                   const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
+                   TO* __restrict__ q_out, TO* __restrict__ cache, float* __restrict__ gate_out,
+                   float* __restrict__ v_first, int v_mode, const float* __restrict__ lambda,
+                   int H, int G, int dk, int dv, int P, int* status) {
+    pdl_enter(TR_QKV_PREPARE);
+    const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const float* in = proj + (size_t)t * ld;
+    const int half = rot / 2;
+    const int page = block_table[(size_t)slot * max_blocks + pos / P];
+    TO* kdst = nullptr;
+    TO* vdst = nullptr;
+    if (page < 0) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    } else {
+        TO* base = cache + (size_t)page * G * P * (dk + dv);
+        kdst = base + (size_t)(pos % P) * dk;
+        vdst = base + (size_t)G * P * dk + (size_t)(pos % P) * dv;
+    }
+    // q and k: one item per pair of rotated elements and per element behind the rotated part
+    const int per_head = dk - half;
+    for (int idx = threadIdx.x; idx < (H + G) * per_head; idx += blockDim.x) {
+        const int head = idx / per_head, j = idx % per_head;
+        const int col = head * dk;
+        const int i0 = j < half ? j : j + half;
+        float a = in[col + i0] + (bias ? bias[col + i0] : 0.f), b = 0.f;
+        if (j < half) {
+            b = in[col + i0 + half] + (bias ? bias[col + i0 + half] : 0.f);
+            float s, c;
+            sincosf((float)pos * inv_freq[j], &s, &c);
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+        }
+        TO* dst = head < H ? q_out + ((size_t)t * H + head) * dk
+                           : (kdst ? kdst + (size_t)(head - H) * P * dk : nullptr);
+        if (dst) {
+            dst[i0] = from_float<TO>(a);
+            if (j < half) dst[i0 + half] = from_float<TO>(b);
+        }
+    }
+    const int vcol = (H + G) * dk;
+    const float lam = v_mode == 2 ? lambda[0] : 0.f;
+    for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) {
+        float v = in[vcol + idx] + (bias ? bias[vcol + idx] : 0.f);
+        if (v_mode == 1) v_first[(size_t)t * G * dv + idx] = v;
+        else if (v_mode == 2) v = (1.f - lam) * v + lam * v_first[(size_t)t * G * dv + idx];
+        if (vdst) vdst[(size_t)(idx / dv) * P * dv + idx % dv] = from_float<TO>(v);
+    }
+    if (gate_out) {
+        const int gcol = vcol + G * dv;
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float z = in[gcol + h] + (bias ? bias[gcol + h] : 0.f);
+            gate_out[(size_t)t * H + h] = 1.f / (1.f + expf(-z));
+        }
+    }
+}
+
+}  // namespace air
+
+AIR_API int air_qkv_prepare(const float* proj, int ld, const float* bias, const float* inv_freq, int rot,
+                            const int* positions, const int* token_seq, const int* block_table, int max_blocks,
+                            void* q_out, void* cache, int out_dtype, float* gate_out, float* v_first, int v_mode,
+                            const float* lambda, int T, int H, int G, int dk, int dv, int P, int* status,
+                            cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > dk || (rot & 1) || (rot > 0 && !inv_freq) || v_mode < 0 || v_mode > 2 ||
+        (v_mode && !v_first) || (v_mode == 2 && !lambda))
+        return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(out_dtype, TO, return air::launch(air::qkv_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, bias,
+                                                   inv_freq, rot, positions, token_seq, block_table, max_blocks,
+                                                   (TO*)q_out, (TO*)cache, gate_out, v_first, v_mode, lambda, H, G, dk,
+                                                   dv, P, status));
+    return 0;
+}
+
+AIR_API int air_trace_set_attention_prepare(unsigned long long* buffer) { return air::set_trace_here(buffer); }

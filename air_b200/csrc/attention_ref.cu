@@ -9,9 +9,12 @@
 // position and on the cache's contents, not on how the tokens were cut into steps or on
 // what else is in the batch.
 //
-// q, out: [T, H, d].  cache: [page, 2, K, P, d] (keys then values).  block_table: [slots, max_blocks],
-// row token_seq[t] for token t (negative: padding, skipped).
+// q: [T, H, d], out: [T, H, dv].  cache: a page holds the keys [K, P, d] and behind them the values [K, P, dv]
+// (with dv == d that is [page, 2, K, P, d]).  block_table: [slots, max_blocks], row token_seq[t] for token t
+// (negative: padding, skipped).
 // A query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys).
+// score = scale * q.k, and with softcap > 0 then softcap * tanh(score / softcap).  With `gate` [T, H] (float32) a
+// head's output is multiplied by its token's gate.
 #include "common.cuh"
 
 namespace air {
@@ -24,7 +27,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
                            const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ token_seq, const int* __restrict__ positions,
-                           T* __restrict__ out, int H, int K, int d, int P, int window, float scale) {
+                           T* __restrict__ out, const float* __restrict__ gate, int H, int K, int d, int dv, int P,
+                           int window, float scale, float softcap) {
     __shared__ float sq[ATT_MAX_D];
     __shared__ float sm[ATT_WARPS], sl[ATT_WARPS];
     __shared__ float sacc[ATT_WARPS][ATT_MAX_D];
@@ -40,26 +44,28 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
     for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = to_float(q[((size_t)t * H + h) * d + i]);
     __syncthreads();
 
-    const int chunks = (d + 31) / 32;
+    const int chunks = (dv + 31) / 32;
     float acc[ATT_MAX_D / 32];
 #pragma unroll
     for (int c = 0; c < ATT_MAX_D / 32; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    const size_t page_stride = (size_t)2 * K * P * d;
+    const size_t page_stride = (size_t)K * P * (d + dv);
     const size_t v_offset = (size_t)K * P * d;
     for (int b = (lo / 32 / ATT_WARPS) * ATT_WARPS + warp; b * 32 <= pos; b += ATT_WARPS) {
         const int key = b * 32 + lane;
         const bool valid = key >= lo && key <= pos;
-        size_t base = 0;
+        size_t base = 0;      // of the key's value
         float s = -INFINITY;
         if (valid) {
             const int page = bt[key / P];
-            base = (size_t)page * page_stride + ((size_t)kvh * P + (size_t)(key % P)) * d;
-            const T* kp = cache + base;
+            const size_t place = (size_t)kvh * P + (size_t)(key % P);
+            base = (size_t)page * page_stride + v_offset + place * dv;
+            const T* kp = cache + (size_t)page * page_stride + place * d;
             float dot = 0.f;
             for (int i = 0; i < d; ++i) dot = fmaf(sq[i], to_float(kp[i]), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float bm = warp_max(s);
         if (bm == -INFINITY) continue;  // the whole block is outside the window
@@ -74,11 +80,11 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)base, j);
             if (pj == 0.f) continue;  // same for the whole warp
-            const T* vp = cache + bj + v_offset;
+            const T* vp = cache + bj;
 #pragma unroll
             for (int c = 0; c < ATT_MAX_D / 32; ++c) {
                 const int i = c * 32 + lane;
-                if (c < chunks && i < d) acc[c] = fmaf(pj, to_float(vp[i]), acc[c]);
+                if (c < chunks && i < dv) acc[c] = fmaf(pj, to_float(vp[i]), acc[c]);
             }
         }
     }
@@ -86,7 +92,7 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
 #pragma unroll
     for (int c = 0; c < ATT_MAX_D / 32; ++c) {
         const int i = c * 32 + lane;
-        if (c < chunks && i < d) sacc[warp][i] = acc[c];
+        if (c < chunks && i < dv) sacc[warp][i] = acc[c];
     }
     __syncthreads();
     float mm = -INFINITY;
@@ -97,11 +103,11 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
         weight[w] = sm[w] == -INFINITY ? 0.f : expf(sm[w] - mm);
         total += sl[w] * weight[w];
     }
-    const float inv = 1.f / total;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float inv = (gate ? gate[(size_t)t * H + h] : 1.f) / total;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < ATT_WARPS; ++w) o += sacc[w][i] * weight[w];
-        out[((size_t)t * H + h) * d + i] = from_float<T>(o * inv);
+        out[((size_t)t * H + h) * dv + i] = from_float<T>(o * inv);
     }
 }
 
@@ -109,15 +115,16 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
 
 AIR_API int air_paged_attention_ref(const void* q, const void* cache, int dtype, const int* block_table,
                                     int max_blocks, const int* token_seq, const int* positions, void* out,
-                                    int T, int H, int K, int d, int P, int window, float scale,
-                                    cudaStream_t stream) {
+                                    const float* gate, int T, int H, int K, int d, int dv, int P, int window,
+                                    float scale, float softcap, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d <= 0 || d > air::ATT_MAX_D || H <= 0 || K <= 0 || H > 65535) return AIR_ERR_BAD_ARGUMENT;
+    if (d <= 0 || d > air::ATT_MAX_D || dv <= 0 || dv > air::ATT_MAX_D || H <= 0 || K <= 0 || H > 65535)
+        return AIR_ERR_BAD_ARGUMENT;
     dim3 grid(T, H);
     AIR_DISPATCH(dtype, TT, {
         return air::launch(air::paged_attention_ref_kernel<TT>, grid, air::ATT_WARPS * 32, 0, stream, (const TT*)q,
-                           (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, H, K, d, P,
-                           window, scale);
+                           (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, gate, H, K, d,
+                           dv, P, window, scale, softcap);
     });
     return 0;
 }

@@ -1,0 +1,87 @@
+// Two row-wise operations of blocks whose sub-layers stand side by side and of gated feed-forwards with limits.
+//
+//   glu_kernel          out[t, i] = g' * sigmoid(alpha * g') * (u' + shift), with g' = min(gate, limit) and
+//                       u' = clamp(up, -limit, limit) where limit > 0 (else gate and up as they are).  alpha = 1,
+//                       shift = 0, limit = 0 is SiLU(gate) * up.  The input [T, 2I] holds blocks of `block` gate
+//                       columns and `block` up columns in turn.
+//   scaled_norm_kernel  x = h + sa * a + sb * b (float32; a scale per column, each term optional), written back into
+//                       the stream h when no rows are named, and out = x / sqrt(mean(x^2) + eps) * w.  With `rows`
+//                       the kernel reads h[rows[r]] and leaves h alone.  Without w it only completes the stream.
+#include "common.cuh"
+
+namespace air {
+
+template <typename TI, typename TO>
+__global__ void glu_kernel(const TI* __restrict__ in, TO* __restrict__ out, int I, int block, size_t total,
+                           float alpha, float limit, float shift) {
+    pdl_enter(TR_GLU);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx % I);
+        const TI* row = in + t * 2 * (size_t)I + (size_t)(i / block) * 2 * block;
+        float g = to_float(row[i % block]), u = to_float(row[block + i % block]);
+        if (limit > 0.f) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+        }
+        out[idx] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+template <typename TW, typename TO>
+__global__ void scaled_norm_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ sa,
+                                   const float* __restrict__ b, const float* __restrict__ sb,
+                                   const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
+                                   int E, float eps) {
+    __shared__ float scratch[32];
+    extern __shared__ float xrow[];
+    pdl_enter(TR_SCALED_NORM);
+    const int r = blockIdx.x;
+    const size_t src = (size_t)(rows ? rows[r] : r) * E;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) {
+        float x = h[src + i];
+        if (a) x += (sa ? sa[i] : 1.f) * a[src + i];
+        if (b) x += (sb ? sb[i] : 1.f) * b[src + i];
+        xrow[i] = x;
+        ss += x * x;
+        if (!rows && (a || b)) h[src + i] = x;
+    }
+    if (!w) return;
+    const float total = block_sum(ss, scratch);
+    const float scale = rsqrtf(total / (float)E + eps);
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+        out[(size_t)r * E + i] = from_float<TO>(xrow[i] * scale * to_float(w[i]));
+}
+
+}  // namespace air
+
+AIR_API int air_glu(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int block, float alpha,
+                    float limit, float shift, cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    if (block <= 0 || I % block) return AIR_ERR_BAD_ARGUMENT;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    AIR_DISPATCH(in_dtype, TI, AIR_DISPATCH(out_dtype, TO, {
+        return air::launch(air::glu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, I, block, total,
+                           alpha, limit, shift);
+    }));
+    return 0;
+}
+
+AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, const float* b, const float* sb, const void* w,
+                            int w_dtype, void* out, int out_dtype, const int* rows, int R, int E, float eps,
+                            cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const int threads = E >= 1024 ? 256 : 128;
+    const size_t smem = sizeof(float) * (size_t)E;
+    if (smem > 200 * 1024) return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
+        auto kernel = air::scaled_norm_kernel<TW, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return air::launch(kernel, R, threads, smem, stream, h, a, sa, b, sb, (const TW*)w, (TO*)out, rows, E, eps);
+    }));
+    return 0;
+}
+
+AIR_API int air_trace_set_gated_ops(unsigned long long* buffer) { return air::set_trace_here(buffer); }

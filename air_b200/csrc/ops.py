@@ -27,8 +27,21 @@ _SIGNATURES = {
     "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "air_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
     "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                        c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                        c_void_p, c_void_p],
+    "air_short_conv_silu": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_int, c_void_p],
+    "air_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                        c_float, c_float, c_int, c_float, c_void_p],
+    "air_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
+                          c_void_p],
+    "air_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    "air_scaled_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                        c_int, c_int, c_float, c_void_p],
     "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_decode_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -79,7 +92,8 @@ def set_pdl(on: bool) -> None:
 
 TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_mul", 5: "convert", 6: "table_update",
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
-               12: "gemm_tc", 13: "sample"}
+               12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
+               17: "qkv_prepare", 18: "glu", 19: "scaled_norm"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -291,20 +305,215 @@ def gemm_f32(a, w, bias, out):
     return out
 
 
-def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window, scale):
+def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window, scale, softcap=0.0, gate=None,
+                        kv_heads=None, page_tokens=None):
+    """Causal attention over the pages with 32-bit arithmetic, for any batch.  q [T, H, d], out [T, H, dv].
+    cache [page, 2, K, P, d] where dv == d; where keys and values differ in size a page is flat: the keys
+    [K, P, d], then the values [K, P, dv], and kv_heads and page_tokens say what K and P are.  score = scale * q.k,
+    then softcap * tanh(score / softcap) where softcap > 0; gate (float32 [T, H]) multiplies a head's output."""
     T, H, d = q.shape
+    dv = out.shape[2]
     _req(q, "q", _FLOATS)
-    _req(cache, "cache", (q.dtype,), (None, 2, None, None, d))
+    if cache.dim() == 5:
+        _req(cache, "cache", (q.dtype,), (None, 2, None, None, d))
+        K, P = cache.shape[2], cache.shape[3]
+        if dv != d:
+            raise KernelError("paged_attention_ref: pages of the shape [2, K, P, d] hold values of the keys' size")
+    else:
+        K, P = int(kv_heads), int(page_tokens)
+        _req(cache, "cache", (q.dtype,), (None, K * P * (d + dv)))
     _req(block_table, "block_table", _I32)
     _req(token_seq, "token_seq", _I32, (T,))
     _req(positions, "positions", _I32, (T,))
-    _req(out, "out", (q.dtype,), (T, H, d))
-    if d % 16 or d > 256:
-        raise KernelError(f"head size {d}: the attention kernels take multiples of 16 up to 256")
+    _req(out, "out", (q.dtype,), (T, H, dv))
+    if gate is not None:
+        _req(gate, "gate", (torch.float32,), (T, H))
+    if d > 256 or dv > 256:
+        raise KernelError(f"head sizes {d} and {dv}: the 32-bit attention kernel takes up to 256")
     _check(_get("air_paged_attention_ref")(
         q.data_ptr(), cache.data_ptr(), _DT[q.dtype], block_table.data_ptr(), block_table.shape[1],
-        token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), T, H, cache.shape[2], d, cache.shape[3],
-        int(window or 0), float(scale), _stream()), "paged_attention_ref")
+        token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(gate), T, H, K, d, dv, P,
+        int(window or 0), float(scale), float(softcap or 0.0), _stream()), "paged_attention_ref")
+    return out
+
+
+def qkv_prepare(proj, bias, inv_freq, positions, token_seq, block_table, q_out, cache, kv_heads, v_dim, page_tokens,
+                gate_out=None, v_first=None, v_mode=0, v_lambda=None, status=None):
+    """From the fused projection of an attention layer to what its attention kernel reads.  proj float32 [T, W]:
+    per token q (H heads of dk), k (G heads of dk), v (G heads of dv) and, with gate_out, H gate logits.  Adds the
+    bias (float32 [W]), rotates the first 2 * len(inv_freq) elements of each head of q and k (element i with
+    i + rot/2, angle position * inv_freq[i] in 32-bit), writes q to q_out [T, H, dk] and k and v into the pages
+    (a page: keys [G, P, dk], then values [G, P, dv]) and sigmoid(gate logits) to gate_out (float32 [T, H]).
+    v_mode 1 also hands the values on in v_first (float32 [T, G * dv]); v_mode 2 first mixes them with v_first:
+    v = (1 - v_lambda) v + v_lambda v_first (v_lambda: a float32 tensor of one element)."""
+    T, H, dk = q_out.shape
+    G, dv, P = int(kv_heads), int(v_dim), int(page_tokens)
+    W = (H + G) * dk + G * dv + (H if gate_out is not None else 0)
+    _req(proj, "proj", (torch.float32,), (T, W))
+    if bias is not None:
+        _req(bias, "bias", (torch.float32,), (W,))
+    rot = 0
+    if inv_freq is not None:
+        _req(inv_freq, "inv_freq", (torch.float32,))
+        rot = 2 * inv_freq.numel()
+        if rot > dk:
+            raise KernelError(f"rotary width {rot} does not fit head size {dk}")
+    _req(positions, "positions", _I32, (T,))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(block_table, "block_table", _I32)
+    _req(q_out, "q_out", _FLOATS)
+    _req(cache, "cache", (q_out.dtype,))
+    if cache[0].numel() != G * P * (dk + dv):
+        raise KernelError(f"qkv_prepare: a page of {cache[0].numel()} elements, not {G} x {P} x ({dk} + {dv})")
+    if gate_out is not None:
+        _req(gate_out, "gate_out", (torch.float32,), (T, H))
+    if v_mode:
+        _req(v_first, "v_first", (torch.float32,), (T, G * dv))
+    if v_mode == 2:
+        _req(v_lambda, "v_lambda", (torch.float32,))
+    _check(_get("air_qkv_prepare")(
+        proj.data_ptr(), W, _ptr(bias), _ptr(inv_freq), rot, positions.data_ptr(), token_seq.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], q_out.data_ptr(), cache.data_ptr(), _DT[q_out.dtype],
+        _ptr(gate_out), _ptr(v_first) if v_mode else None, int(v_mode), _ptr(v_lambda) if v_mode == 2 else None,
+        T, H, G, dk, dv, P, _ptr(status), _stream()), "qkv_prepare")
+    return q_out
+
+
+def _columns(t, name):
+    """(pointer, row stride) of a float32 matrix whose rows may be a band of columns of a wider one."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be a float32 CUDA matrix with contiguous rows")
+    return t.data_ptr(), t.stride(0)
+
+
+def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
+    """y[t, c] = silu(sum_j weight[c, j] x[t - (taps - 1 - j), c]) for every entry of the batch (rows q_start[e] ..
+    q_start[e + 1], state row slots[e]): a causal convolution over the request's tokens, whose inputs before the
+    portion come from state [slots, C, taps - 1] (oldest first; zeros at a request's start) and whose last taps - 1
+    inputs are left there.  x: float32 [T, C] (may be a band of columns of a wider matrix); y: float32 [T, C].
+    max_tokens: the longest portion of the batch (a host number: it sizes the grid)."""
+    C, taps = weight.shape
+    xp, ld = _columns(x, "x")
+    _req(weight, "weight", (torch.float32,))
+    _req(state, "state", (torch.float32,), (None, C, taps - 1))
+    _req(y, "y", (torch.float32,), (x.shape[0], C))
+    _req(q_start, "q_start", _I32)
+    _req(slots, "slots", _I32)
+    if x.shape[1] != C:
+        raise KernelError(f"short_conv_silu: x has {x.shape[1]} channels, the weight {C}")
+    if not (1 <= taps <= 8):
+        raise KernelError(f"short_conv_silu: {taps} taps (the kernel takes 1 to 8)")
+    _check(_get("air_short_conv_silu")(xp, ld, weight.data_ptr(), state.data_ptr(), y.data_ptr(), q_start.data_ptr(),
+                                       slots.data_ptr(), slots.shape[0], C, taps, int(max_tokens), _stream()),
+           "short_conv_silu")
+    return y
+
+
+SCAN_DELTA, SCAN_GLA = 0, 1
+
+
+def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, q_scale=1.0, beta=None, a_log=None, dt_bias=None,
+                tau=1.0, unit=False, unit_eps=1e-6):
+    """A state S [d, dv] per head and request, updated token by token in 32-bit and read out after each update.
+    q, k float32 [T, G * d], v [T, H * dv] (each may be a band of columns of a wider matrix); head h reads q/k head
+    h // (H / G); state [slots, H, d, dv]; out [T, H, dv].
+    SCAN_DELTA: decay, beta [T, H] logits; g = exp(-exp(a_log[h]) * softplus(decay + dt_bias[h])), b = sigmoid(beta);
+      with unit, q and k are first divided by sqrt(sum of squares + unit_eps), q then multiplied by q_scale;
+      S = g S; u = b (v - S^T k); S += k u^T; o = S^T q.
+    SCAN_GLA: decay [T, H * d] logits; alpha = sigmoid(decay)^(1 / tau); q is multiplied by q_scale;
+      S = diag(alpha) S + k v^T; o = S^T q."""
+    slots_n, H, d, dv = state.shape
+    _req(state, "state", (torch.float32,))
+    T = out.shape[0]
+    _req(out, "out", (torch.float32,), (T, H, dv))
+    qp, ldq = _columns(q, "q")
+    kp, ldk = _columns(k, "k")
+    vp, ldv = _columns(v, "v")
+    dp, ldd = _columns(decay, "decay")
+    if q.shape[1] % d or k.shape != q.shape or v.shape[1] != H * dv:
+        raise KernelError("linear_scan: q, k or v do not fit the state's shape")
+    G = q.shape[1] // d
+    if G == 0 or H % G:
+        raise KernelError(f"linear_scan: {H} heads over {G} heads of q and k")
+    bp, ldb = (None, 0)
+    if mode == SCAN_DELTA:
+        bp, ldb = _columns(beta, "beta")
+        _req(a_log, "a_log", (torch.float32,), (H,))
+        _req(dt_bias, "dt_bias", (torch.float32,), (H,))
+        if decay.shape[1] != H or beta.shape[1] != H:
+            raise KernelError("linear_scan: the delta rule takes one decay and one beta per head")
+    elif mode == SCAN_GLA:
+        if decay.shape[1] != H * d or G != H:
+            raise KernelError("linear_scan: gated linear attention takes a decay per key channel of every head")
+    else:
+        raise KernelError(f"linear_scan: mode {mode}")
+    if d > 1024:
+        raise KernelError(f"linear_scan: {d} key channels per head (the kernel takes up to 1,024)")
+    _req(q_start, "q_start", _I32)
+    _req(slots, "slots", _I32)
+    _check(_get("air_linear_scan")(
+        int(mode), qp, ldq, kp, ldk, vp, ldv, dp, ldd, bp, ldb, _ptr(a_log), _ptr(dt_bias), state.data_ptr(),
+        out.data_ptr(), q_start.data_ptr(), slots.data_ptr(), slots.shape[0], H, G, d, dv, float(q_scale),
+        1.0 / float(tau), 1 if unit else 0, float(unit_eps), _stream()), "linear_scan")
+    return out
+
+
+def gated_rmsnorm(o, gate, weight, eps, out, token_seq):
+    """out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * weight * silu(gate[t, h, :]).  o float32 [T, H, dv]; gate
+    float32 [T, H * dv] (may be a band of columns); weight float32 [dv]; out [T, H * dv]."""
+    T, H, dv = o.shape
+    _req(o, "o", (torch.float32,))
+    gp, ldg = _columns(gate, "gate")
+    if gate.shape != (T, H * dv):
+        raise KernelError("gated_rmsnorm: the gate does not fit")
+    _req(weight, "weight", (torch.float32,), (dv,))
+    _req(out, "out", _FLOATS, (T, H * dv))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _check(_get("air_gated_rmsnorm")(o.data_ptr(), gp, ldg, weight.data_ptr(), out.data_ptr(), _DT[out.dtype],
+                                     token_seq.data_ptr(), T, H, dv, float(eps), _stream()), "gated_rmsnorm")
+    return out
+
+
+def glu(gate_up, out, block=None, alpha=1.0, limit=0.0, shift=0.0):
+    """out[t, i] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)
+    where limit > 0; gate_up [T, 2I] as silu_mul takes it."""
+    T, I = out.shape
+    block = I if block is None else block
+    if block <= 0 or I % block:
+        raise KernelError(f"glu: block {block} does not divide {I}")
+    _req(gate_up, "gate_up", _FLOATS, (T, 2 * I))
+    _req(out, "out", _FLOATS)
+    _check(_get("air_glu")(gate_up.data_ptr(), _DT[gate_up.dtype], out.data_ptr(), _DT[out.dtype], T, I, block,
+                           float(alpha), float(limit), float(shift), _stream()), "glu")
+    return out
+
+
+def scaled_norm(h, terms, weight, eps, out, rows=None):
+    """x = h + sum of scale * term over up to two terms (term float32 [T, E], scale float32 [E] or None), written
+    into h when rows is None; out = x / sqrt(mean(x^2) + eps) * weight.  With rows: out[r] is that of row rows[r],
+    h unchanged.  weight None (and out None): only the stream is completed."""
+    E = h.shape[-1]
+    _req(h, "h", (torch.float32,), (None, E))
+    terms = list(terms)
+    if len(terms) > 2:
+        raise KernelError("scaled_norm: at most two terms")
+    ptrs = []
+    for term, scale in terms + [(None, None)] * (2 - len(terms)):
+        if term is not None:
+            _req(term, "term", (torch.float32,), tuple(h.shape))
+        if scale is not None:
+            _req(scale, "scale", (torch.float32,), (E,))
+        ptrs += [_ptr(term), _ptr(scale)]
+    R = h.shape[0] if rows is None else rows.shape[0]
+    if rows is not None:
+        _req(rows, "rows", _I32)
+    if weight is not None:
+        _req(weight, "weight", _FLOATS, (E,))
+        _req(out, "out", _FLOATS, (R, E))
+    _check(_get("air_scaled_norm")(h.data_ptr(), *ptrs, _ptr(weight), _DT[weight.dtype] if weight is not None else 0,
+                                   _ptr(out) if weight is not None else None,
+                                   _DT[out.dtype] if weight is not None else 0, _ptr(rows), R, E, float(eps),
+                                   _stream()), "scaled_norm")
     return out
 
 

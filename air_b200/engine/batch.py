@@ -56,6 +56,9 @@ class StepContext:
     plans: Dict[Hashable, SimpleNamespace] = field(default_factory=dict)
                                                 # what the parts planned for this step (Part.plan), by plan key:
                                                 # their int32 arrays as device tensors, their host values
+    shared: Dict[Hashable, object] = field(default_factory=dict)
+                                                # what the layers of this step hand to one another (the values of
+                                                # an earlier layer, say); emptied when a forward pass begins
     residual: Optional[torch.Tensor] = None     # [T, hidden] float32, set by the block that runs: a mixer or a
                                                 # feed-forward may add its output into it (in 32-bit) and return
                                                 # None instead of returning the output for the next norm to add

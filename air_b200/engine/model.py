@@ -104,6 +104,7 @@ class Model:
         """Runs the batch's tokens through every run of the order list, writing the caches,
         and returns float32 logits [wanted rows, vocab]."""
         rt = self.rt
+        ctx.shared.clear()
         h = torch.empty((ctx.num_tokens, self.spec.hidden_size), dtype=torch.float32, device=rt.device)
         ops.embedding(self.embedding, ctx.token_ids, h, status=ctx.status, last_token=ctx.last_token,
                       multiplier=self.spec.embedding_multiplier)

@@ -56,7 +56,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (whole pages per request)")
     ap.add_argument("--page-tokens", type=int, default=64, help="tokens per cache page (a divisor of 64)")
-    ap.add_argument("--max-requests", type=int, default=8)
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: live requests at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     engine = Engine.from_folder(args.model, EngineConfig(

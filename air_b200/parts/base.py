@@ -107,14 +107,19 @@ class SlotStateView:
 class PagedKV(CacheNeed):
     """Keys and values of every token, in pages.  window: None keeps all keys, a number
     keeps the last `window` of them (older pages are given back).  Layers with equal needs
-    share a group: one pool of pages and one block table."""
+    share a group: one pool of pages and one block table.  v_dim: the size of a value where it
+    differs from a key's (head_dim); a page is then flat, the keys [kv_heads, page_tokens, head_dim]
+    followed by the values [kv_heads, page_tokens, v_dim]."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_dim: Optional[int] = None
     paged = True
 
     def page_shape(self, page_tokens):
-        return (2, self.kv_heads, page_tokens, self.head_dim)
+        if self.v_dim is None or self.v_dim == self.head_dim:
+            return (2, self.kv_heads, page_tokens, self.head_dim)
+        return (self.kv_heads * page_tokens * (self.head_dim + self.v_dim),)
 
     def view(self, tensor, group):
         return PagedKVView(tensor, group, self)
@@ -184,6 +189,14 @@ class PreNormed:
         return self.x.device
 
 
+@dataclass
+class ScaledSum:
+    """What parts that stand side by side add to the stream together: the sum of scale * term over `terms`, a list
+    of (float32 [T, hidden], float32 [hidden] or None: a scale per column).  A form of a norm's `delta`: the norm
+    that follows completes the stream with it (Norm.add_delta, or a kernel of its own that also normalises)."""
+    terms: list
+
+
 class Part:
     # True if forward() only launches work on the current stream from device data (no host
     # reads of the batch or of a result), so that a decode step can be captured in a CUDA graph.
@@ -222,7 +235,10 @@ class Norm(Part):
         """h += delta for every form of delta that a part may hand on (see the module's text)."""
         if delta is not None:
             from ..csrc import ops
-            ops.add_parts(h, delta)
+            if isinstance(delta, ScaledSum):
+                ops.scaled_norm(h, delta.terms, None, 0.0, None)
+            else:
+                ops.add_parts(h, delta)
         return h
 
 
@@ -230,6 +246,11 @@ class PositionEncoding(Part):
     rotary_dim: int = 0
 
     def table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def frequencies(self) -> Optional[torch.Tensor]:
+        """float32 [rotary_dim / 2]: the angle of pair i at position p is p * frequencies[i], for mixers whose
+        kernels evaluate the angles themselves instead of reading a table (no bound on the position)."""
         return None
 
 

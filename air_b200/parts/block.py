@@ -79,3 +79,53 @@ class PreNormBlock(Block):
         a = self.mixer.forward(x, ctx, cache, owns_cache)      # None: the mixer has added its output to h itself
         x = self._norm(self.ff_norm, h, a, self.feed_forward, ctx)
         return h, self.feed_forward.forward(x, ctx)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """x = norm(h); h = h + s_m * mixer(x) + s_f * feed_forward(x): one norm whose rows both sub-layers read, their
+    outputs added to the stream together, each first multiplied by a learned scale per column (layer scale).
+    Roles: norm, mixer, feed_forward (may be absent: a layer of a mixer only).  spec.names may also give
+    "mixer_scale" and "feed_forward_scale", what follows the layer's prefix in the names of the two scale vectors
+    [hidden]; a scale that is not named is 1.
+
+    The block hands its two outputs on as a ScaledSum: the next block's norm (or the model's last one) completes the
+    stream with them in 32-bit in the kernel that normalises."""
+
+    def __init__(self, spec: BlockSpec):
+        super().__init__(spec)
+        self.norm = NORMS.get(spec.part("norm").kind)(spec.part("norm"), spec.name("norm"))
+        self.mixer = MIXERS.get(spec.part("mixer").kind)(spec.part("mixer"), spec.name("mixer"))
+        self.feed_forward = None
+        if "feed_forward" in spec.parts:
+            self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
+                                                                                  spec.name("feed_forward"))
+        self.scale_names = {role: spec.prefix + spec.names[role + "_scale"] for role in ("mixer", "feed_forward")
+                            if role + "_scale" in spec.names and (role == "mixer" or self.feed_forward is not None)}
+        self.scales = {}
+
+    def parts(self):
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    def tensor_specs(self):
+        from ..weights.loader import TensorSpec
+        size = self.spec.part("norm")["size"]
+        return super().tensor_specs() + [TensorSpec(name, (size,), init="one_plus_normal", wide=True)
+                                         for name in self.scale_names.values()]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        import torch
+        self.scales = {role: tensors[name].to(torch.float32).contiguous() for role, name in self.scale_names.items()}
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, h, pending, ctx, cache, owns_cache=True):
+        from .base import ScaledSum
+        ctx.residual = None          # the sub-layers' outputs are scaled before they are added: they return them
+        x = self.norm.forward(h, pending)
+        terms = [(self.mixer.forward(x, ctx, cache, owns_cache), self.scales.get("mixer"))]
+        if self.feed_forward is not None:
+            terms.append((self.feed_forward.forward(x, ctx), self.scales.get("feed_forward")))
+        return h, ScaledSum(terms)

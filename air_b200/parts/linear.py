@@ -100,6 +100,11 @@ class Linear:
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
         return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status, **scale)
 
+    def f32(self, x: torch.Tensor) -> torch.Tensor:
+        """float32 [rows, out], complete sums: the tcgen05 kernel in one pass for few rows of 16-bit weights, else the
+        product that __call__ picks."""
+        return self.full(x) if self.small(x) else self(x, torch.float32)
+
     def adds_into(self, x: torch.Tensor, residual) -> bool:
         """Whether add_into() applies: 16-bit weights, a float32 stream of this product's shape."""
         return (residual is not None and self.weight.dtype != torch.float32 and x.dtype == self.weight.dtype

@@ -52,15 +52,17 @@ class SwiGLU(FeedForward):
 
     graph_safe = True
 
+    # what follows the prefix in the names of the three matrices
+    NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+
     def tensor_specs(self):
-        e, i, p = self.spec["hidden"], self.spec["intermediate"], self.prefix
-        return [TensorSpec(p + "gate_proj.weight", (i, e)), TensorSpec(p + "up_proj.weight", (i, e)),
-                TensorSpec(p + "down_proj.weight", (e, i))]
+        e, i, p, n = self.spec["hidden"], self.spec["intermediate"], self.prefix, self.NAMES
+        return [TensorSpec(p + n["gate"], (i, e)), TensorSpec(p + n["up"], (i, e)), TensorSpec(p + n["down"], (e, i))]
 
     def load(self, tensors, rt):
         super().load(tensors, rt)
         p = self.prefix
-        g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        g, u = tensors[p + self.NAMES["gate"]], tensors[p + self.NAMES["up"]]
         if g.dtype != u.dtype:
             raise ValueError(f"{p}: gate and up projections are stored in different precisions")
         inter = self.intermediate = self.spec["intermediate"]
@@ -74,7 +76,7 @@ class SwiGLU(FeedForward):
             w = torch.stack([g.view(inter // block, block, -1), u.view(inter // block, block, -1)], dim=1)
             w = w.reshape(2 * inter, -1)
         self.gate_up = Linear(w.contiguous(), rt.status, gate_up_block=block if block != inter else 0)
-        self.down = Linear(tensors[p + "down_proj.weight"], rt.status)
+        self.down = Linear(tensors[p + self.NAMES["down"]], rt.status)
 
     def accepts_prenormed(self, ctx, owns_cache=True):
         return self.rt.dtype == torch.bfloat16 and self.gate_up.takes_prenormed(ctx.num_tokens, silu=True)
@@ -95,3 +97,25 @@ class SwiGLU(FeedForward):
         if self.down.adds_into(act, residual):
             return self.down.add_into(act, residual)
         return self.down(act, torch.float32)
+
+
+@register_feed_forward("clamped_glu")
+class ClampedGLU(SwiGLU):
+    """down(g * sigmoid(alpha * g) * (u + 1)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit): a
+    gated feed-forward whose gate is cut from above, whose linear branch is cut on both sides and shifted by one,
+    and whose sigmoid is sharpened by alpha (1.702 gives the sigmoid form of GELU).
+    params: hidden, intermediate, limit, alpha.  Tensors: <prefix>gate, up [intermediate, hidden], down
+    [hidden, intermediate].  gate and up are one matrix as in SwiGLU; the activation is a kernel of its own that
+    reads the same arrangement."""
+
+    NAMES = {"gate": "gate", "up": "up", "down": "down"}
+
+    def accepts_prenormed(self, ctx, owns_cache=True):
+        return False
+
+    def forward(self, x, ctx):
+        gu = self.gate_up.f32(x)
+        act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
+        ops.glu(gu, act, block=self.block, alpha=float(self.spec.get("alpha", 1.702)),
+                limit=float(self.spec["limit"]), shift=1.0)
+        return self.down.f32(act)

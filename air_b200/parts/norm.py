@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, PreNormed
+from .base import Norm, PreNormed, ScaledSum
 from .registry import register_norm
 
 
@@ -13,17 +13,18 @@ from .registry import register_norm
 class RMSNorm(Norm):
     """x * rsqrt(mean(x^2) + eps) * w, product order x*scale*w, no bias, no offset on w
     (AIR: src/reference/reference_executor.cpp:17-27; src/cuda/cuda_backend.cu:789-831).
-    params: size, eps.  Tensor: <prefix>weight [size].  The sum of squares and the residual
-    sum are 32-bit."""
+    params: size, eps; tensor: what follows the prefix in the weight's name ("weight" unless given).
+    Tensor: <prefix><tensor> [size].  The sum of squares and the residual sum are 32-bit."""
 
     graph_safe = True
 
     def tensor_specs(self):
-        return [TensorSpec(self.prefix + "weight", (self.spec["size"],), init="one_plus_normal", wide=True)]
+        return [TensorSpec(self.prefix + self.spec.get("tensor", "weight"), (self.spec["size"],),
+                           init="one_plus_normal", wide=True)]
 
     def load(self, tensors, rt):
         super().load(tensors, rt)
-        self.weight = tensors[self.prefix + "weight"]
+        self.weight = tensors[self.prefix + self.spec.get("tensor", "weight")]
         self.eps = float(self.spec["eps"])
 
     prenorm = True      # x * scale(row) * w: forward_prenormed writes bfloat16(x * w) and leaves the scale to the consumer
@@ -31,12 +32,19 @@ class RMSNorm(Norm):
     def forward(self, h, delta, rows=None):
         n = h.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, h.shape[1]), dtype=self.rt.dtype, device=h.device)
+        if isinstance(delta, ScaledSum):
+            # the outputs of sub-layers that stand side by side, each with its scale per column: one kernel
+            # completes the stream with them and normalises
+            return ops.scaled_norm(h, delta.terms, self.weight, self.eps, out, rows=rows)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, out, rows=rows)
 
     def forward_prenormed(self, h, delta) -> PreNormed:
         """As forward() without rows, for a part that takes its input as PreNormed: the stream is completed and
         the rows are written short of their scale, by many small blocks that do not wait for one another."""
         T, E = h.shape
+        if isinstance(delta, ScaledSum):
+            self.add_delta(h, delta)
+            delta = None
         xg = torch.empty((T, E), dtype=torch.bfloat16, device=h.device)
         ss = torch.empty((-(-E // ops.PRENORM_CHUNK), T), dtype=torch.float32, device=h.device)
         ops.add_prenorm(h, delta, self.weight, xg, ss)

@@ -38,6 +38,31 @@ class RopeHalf(PositionEncoding):
         return self._table
 
 
+@register_position_encoding("rope_half_live")
+class RopeHalfLive(PositionEncoding):
+    """The same rotation (pairs (i, i + rot/2), angle p * theta^(-2i/rot)) without a table and so without a
+    longest position: the mixer's kernel multiplies the position by the pair's frequency and takes cos and sin
+    itself, in 32-bit.  params: rotary_dim (may be smaller than the head: the rest passes unchanged), theta.
+    The frequencies are evaluated in 64-bit once and kept as float32 [rotary_dim / 2]."""
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        rot, theta = int(self.spec["rotary_dim"]), float(self.spec["theta"])
+        if rot % 2 or rot < 0:
+            raise ValueError("rope_half_live needs an even rotary width")
+        self.rotary_dim = rot
+        key = ("rope_half_live", rot, theta)
+        f = rt.shared.get(key)
+        if f is None:
+            i = torch.arange(rot // 2, dtype=torch.float64)
+            f = rt.shared[key] = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * i / max(rot, 1)) \
+                .to(torch.float32).to(rt.device)
+        self._frequencies = f
+
+    def frequencies(self):
+        return self._frequencies if self.rotary_dim else None
+
+
 @register_position_encoding("none")
 class NoPosition(PositionEncoding):
     """No position encoding: the mixer's kernel rotates nothing."""
