@@ -319,6 +319,8 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
         K, P = cache.shape[2], cache.shape[3]
         if dv != d:
             raise KernelError("paged_attention_ref: pages of the shape [2, K, P, d] hold values of the keys' size")
+        if d % 16:
+            raise KernelError(f"head size {d}: pages of the shape [2, K, P, d] take multiples of 16 up to 256")
     else:
         K, P = int(kv_heads), int(page_tokens)
         _req(cache, "cache", (q.dtype,), (None, K * P * (d + dv)))

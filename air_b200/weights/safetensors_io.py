@@ -122,6 +122,6 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata=None
         f.write(struct.pack("<Q", len(raw)))
         f.write(raw)
         for name in order:
-            t = tensors[name].detach().to("cpu").contiguous()
+            t = tensors[name].detach().to("cpu").contiguous().reshape(-1)      # (a scalar has no last axis to view)
             f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
     os.replace(tmp, path)
