@@ -50,7 +50,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
                             const int* __restrict__ positions, __nv_bfloat16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, int H, int K, int P, int window,
-                            float scale_log2, int* status) {
+                            float scale_log2, float cap_log2, float cap_pre, int* status) {
+    // cap_log2 > 0: a score s becomes cap * tanh(s * cap_pre) with cap_pre = scale / cap, in units of log2 e
     constexpr int SUB = D / 64;                 // 64-column sub-tiles of a row
     constexpr int SUB_BYTES = DT_TILE * 128;    // 8 KB
     constexpr int STAGE_BYTES = 2 * SUB * SUB_BYTES;
@@ -293,8 +294,13 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
                     for (int e = 0; e < 2; ++e) {
                         const int key = kbase + 8 * j + 2 * tq + e;
                         const bool ok = key >= lo && key <= pos;
-                        s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
-                        s[j][2 + e] = ok ? s[j][2 + e] * scale_log2 : -INFINITY;
+                        if (cap_log2 > 0.f) {
+                            s[j][e] = ok ? cap_log2 * tanhf(s[j][e] * cap_pre) : -INFINITY;
+                            s[j][2 + e] = ok ? cap_log2 * tanhf(s[j][2 + e] * cap_pre) : -INFINITY;
+                        } else {
+                            s[j][e] = ok ? s[j][e] * scale_log2 : -INFINITY;
+                            s[j][2 + e] = ok ? s[j][2 + e] * scale_log2 : -INFINITY;
+                        }
                         tm0 = fmaxf(tm0, s[j][e]);
                         tm1 = fmaxf(tm1, s[j][2 + e]);
                     }
@@ -396,7 +402,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_cache, const
 template <int D>
 int launch_decode_tma(const CUtensorMap& map, const FreshQkv& fresh, const void* q, const int* block_table, int max_blocks,
                       const int* token_seq, const int* positions, void* out, float* part_o, float* part_ml, int T,
-                      int H, int K, int P, int window, float scale, int splits, int* status, cudaStream_t stream) {
+                      int H, int K, int P, int window, float scale, float softcap, int splits, int* status,
+                      cudaStream_t stream) {
     const int head_blocks = (H / K + 15) / 16;
     const size_t ring = (size_t)DT_STAGES * 2 * (D / 64) * DT_TILE * 128;
     const size_t merge = (size_t)(DT_CONSUMERS * 16 * D + 2 * DT_CONSUMERS * 16) * sizeof(float);
@@ -406,7 +413,8 @@ int launch_decode_tma(const CUtensorMap& map, const FreshQkv& fresh, const void*
     if (e != cudaSuccess) return (int)e;
     return launch(kernel, dim3(splits, K * head_blocks, T), DT_THREADS, smem, stream, map, fresh, (const __nv_bfloat16*)q,
                   block_table, max_blocks, token_seq, positions, (__nv_bfloat16*)out, part_o, part_ml, H, K, P, window,
-                  scale * 1.4426950408889634f, status);
+                  scale * 1.4426950408889634f, softcap > 0.f ? softcap * 1.4426950408889634f : 0.f,
+                  softcap > 0.f ? scale / softcap : 0.f, status);
 }
 
 }  // namespace air
@@ -420,7 +428,7 @@ namespace air {
 static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void* cache, long long pages,
                                 const int* block_table, int max_blocks, const int* token_seq, const int* positions,
                                 void* out, float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
-                                float scale, int splits, int* status, cudaStream_t stream) {
+                                float scale, float softcap, int splits, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || K <= 0 || H % K || P % 16 || (P < 64 ? 64 % P : P % 64) || splits < 1 || T > 65535 ||
         (splits > 1 && (!part_o || !part_ml)) || ((uintptr_t)cache & 15))
@@ -432,15 +440,15 @@ static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void
     switch (D) {
         case 64:
             rc = launch_decode_tma<64>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o, part_ml,
-                                       T, H, K, P, window, scale, splits, status, stream);
+                                       T, H, K, P, window, scale, softcap, splits, status, stream);
             break;
         case 128:
             rc = launch_decode_tma<128>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o,
-                                        part_ml, T, H, K, P, window, scale, splits, status, stream);
+                                        part_ml, T, H, K, P, window, scale, softcap, splits, status, stream);
             break;
         case 256:
             rc = launch_decode_tma<256>(map, fresh, q, block_table, max_blocks, token_seq, positions, out, part_o,
-                                        part_ml, T, H, K, P, window, scale, splits, status, stream);
+                                        part_ml, T, H, K, P, window, scale, softcap, splits, status, stream);
             break;
         default:
             return AIR_ERR_BAD_ARGUMENT;
@@ -452,14 +460,14 @@ static int decode_attention_tma(const FreshQkv& fresh, const void* q, const void
 }  // namespace air
 
 // Arguments as air_decode_attention (attention_decode.cu), plus the number of pages of the cache
-// (its first dimension) and the status word.
+// (its first dimension), a soft cap (> 0: score = softcap * tanh(scale * q.k / softcap)) and the status word.
 AIR_API int air_decode_attention_tma(const void* q, const void* cache, long long pages, const int* block_table,
                                      int max_blocks, const int* token_seq, const int* positions, void* out,
                                      float* part_o, float* part_ml, int T, int H, int K, int D, int P, int window,
-                                     float scale, int splits, int* status, cudaStream_t stream) {
+                                     float scale, float softcap, int splits, int* status, cudaStream_t stream) {
     return air::decode_attention_tma(air::FreshQkv{nullptr, 0, 0, nullptr, nullptr, nullptr}, q, cache, pages,
                                      block_table, max_blocks, token_seq, positions, out, part_o, part_ml, T, H, K, D, P,
-                                     window, scale, splits, status, stream);
+                                     window, scale, softcap, splits, status, stream);
 }
 
 // The same from the q/k/v product's output instead of q: qkv float32 [parts][T][(H + 2 K) D] (partial sums that
@@ -475,7 +483,7 @@ AIR_API int air_decode_attention_tma_fresh(const float* qkv, int parts, const fl
     const air::FreshQkv fresh{qkv, parts, (size_t)T * (size_t)(H + 2 * K) * (size_t)D, bias, table,
                               write_kv ? (__nv_bfloat16*)cache : nullptr};
     return air::decode_attention_tma(fresh, nullptr, cache, pages, block_table, max_blocks, token_seq, positions, out,
-                                     part_o, part_ml, T, H, K, D, P, window, scale, splits, status, stream);
+                                     part_o, part_ml, T, H, K, D, P, window, scale, 0.f, splits, status, stream);
 }
 
 AIR_API int air_trace_set_attention_decode_tma(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -59,6 +59,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// tanh by two instructions of the special-function unit: 1 - 2 / (e^(2x) + 1).  The absolute error is about 1e-7
+// (that of the subtraction), which a soft cap multiplies by its width: far below bfloat16's rounding of the
+// probabilities.  e^(2x) = inf gives 1, 0 gives -1.
+__device__ __forceinline__ float fast_tanh(float x) {
+    const float e = fast_exp2(x * 2.8853900817779268f);
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(e + 1.f));
+    return fmaf(-2.f, r, 1.f);
+}
+
 // Two non-negative floats to a pair of bfloat16 (round half up) with integer adds and one byte
 // permute.  The conversion instruction shares the special-function pipe with ex2, which is what
 // this kernel waits for most (79 % busy before this change); the integer pipe is nearly idle.
@@ -107,7 +117,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, int max_blocks, const int* __restrict__ tiles,
                             int n_pairs, const int* __restrict__ segments, int n_slots, float* __restrict__ part_o,
                             float2* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int H, int K, int P,
-                            int window, float scale_log2, int* __restrict__ status) {
+                            int window, float scale_log2, float cap, float cap_pre, int* __restrict__ status) {
+    // cap > 0: a score s becomes cap * tanh(s * cap_pre) (cap_pre = scale / cap) and scale_log2 is log2(e) alone
     constexpr int SUB = D / 64;                            // 64-column (128-byte) sub-tiles per row
     constexpr int Q_BYTES = SUB * AT_BM * 128;             // one row tile of Q
     constexpr int KV_SUB = AT_BN * 128;                    // one sub-tile of K or V
@@ -342,6 +353,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tc_fence_after();
             uint32_t sv[AT_BN];
             tmem_ld64(my_s + b * AT_BN, sv);
+            if (cap > 0.f) {
+#pragma unroll
+                for (int c = 0; c < AT_BN; ++c) sv[c] = __float_as_uint(cap * fast_tanh(__uint_as_float(sv[c]) * cap_pre));
+            }
             const int kbase = (tile0 + me.first + it) * AT_BN;
             // Scores stay as the product left them; the scale goes into the exponent's multiply-add.
             // Only tiles on the diagonal or at a window's edge need the mask (the same for the warp).
@@ -587,7 +602,7 @@ template <int D>
 int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* block_table, int max_blocks,
                       const int* tiles, int n_tiles, const int* segments, int n_segments, const int* items, int n_items,
                       int n_slots, float* part_o, float* part_ml, void* out, int H, int K, int P, int window, float scale,
-                      int* status, cudaStream_t stream) {
+                      float softcap, int* status, cudaStream_t stream) {
     // (more than half of an SM's shared memory, so that two blocks never share its tensor memory)
     size_t smem = 1024 + (size_t)AT_ROW_TILES * (D / 64) * AT_BM * 128 +
                   (size_t)AT_STAGES * 2 * (D / 64) * AT_BN * 128 + 256;
@@ -599,7 +614,8 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
     const dim3 grid = segments ? dim3(n_segments) : dim3(H, n_pairs);
     int rc = launch(kernel, grid, AT_THREADS, smem, stream, mq, mc, block_table, max_blocks, tiles, n_pairs, segments,
                     n_slots, part_o, (float2*)part_ml, (__nv_bfloat16*)out, H, K, P, window,
-                    scale * 1.4426950408889634f, status);
+                    (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f, softcap > 0.f ? softcap : 0.f,
+                    softcap > 0.f ? scale / softcap : 0.f, status);
     if (rc || !segments || n_items <= 0) return rc;
     return launch(prefill_combine_kernel<D>, dim3(n_items, AT_ROW_TILES * AT_BM / 8), 256, 0, stream, tiles, n_pairs,
                   items, n_slots, (const float*)part_o, (const float2*)part_ml, (__nv_bfloat16*)out, H, status);
@@ -608,13 +624,14 @@ int launch_prefill_tc(const CUtensorMap& mq, const CUtensorMap& mc, const int* b
 }  // namespace air
 
 // q [T, H, D] bf16.  tiles: n_tiles entries in groups of 16 per request.  Head size 64 or 128.
+// softcap > 0: scores are scale * q.k, then softcap * tanh(score / softcap).
 // segments (or null: one block per pair and head) [n_segments, 5], items [n_items, 4], part_o float32
 // [n_slots, 256, D] and part_ml float32 [n_slots, 256, 2]: see the head of this file.
 AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, long long pages, const int* block_table,
                                      int max_blocks, const int* tiles, int n_tiles, const int* segments, int n_segments,
                                      const int* items, int n_items, int n_slots, float* part_o, float* part_ml,
-                                     void* out, int H, int K, int D, int P, int window, float scale, int* status,
-                                     cudaStream_t stream) {
+                                     void* out, int H, int K, int D, int P, int window, float scale, float softcap,
+                                     int* status, cudaStream_t stream) {
     using namespace air;
     if (n_tiles <= 0) return 0;
     if (segments && (n_segments <= 0 || n_items < 0 || n_slots < 0 || (n_items > 0 && !items) ||
@@ -631,9 +648,9 @@ AIR_API int air_prefill_attention_tc(const void* q, int T, const void* cache, lo
     if (rc) return rc;
     if (D == 64)
         return launch_prefill_tc<64>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
-                                     n_slots, part_o, part_ml, out, H, K, P, window, scale, status, stream);
+                                     n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream);
     return launch_prefill_tc<128>(mq, mc, block_table, max_blocks, tiles, n_tiles, segments, n_segments, items, n_items,
-                                  n_slots, part_o, part_ml, out, H, K, P, window, scale, status, stream);
+                                  n_slots, part_o, part_ml, out, H, K, P, window, scale, softcap, status, stream);
 }
 
 AIR_API int air_trace_set_attention_prefill_tc(unsigned long long* buffer) { return air::set_trace_here(buffer); }

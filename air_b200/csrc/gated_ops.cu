@@ -4,6 +4,7 @@
 //                       u' = clamp(up, -limit, limit) where limit > 0 (else gate and up as they are).  alpha = 1,
 //                       shift = 0, limit = 0 is SiLU(gate) * up.  The input [T, 2I] holds blocks of `block` gate
 //                       columns and `block` up columns in turn.
+//   head_gate_kernel    x[t, h, :] *= gate[t, h], for attention kernels that do not multiply by a gate as they write
 //   scaled_norm_kernel  x = h + sa * a + sb * b (float32; a scale per column, each term optional), written back into
 //                       the stream h when no rows are named, and out = x / sqrt(mean(x^2) + eps) * w.  With `rows`
 //                       the kernel reads h[rows[r]] and leaves h alone.  Without w it only completes the stream.
@@ -25,6 +26,18 @@ __global__ void glu_kernel(const TI* __restrict__ in, TO* __restrict__ out, int 
             u = fminf(fmaxf(u, -limit), limit);
         }
         out[idx] = from_float<TO>(g / (1.f + expf(-alpha * g)) * (u + shift));
+    }
+}
+
+// x [T, H, d] *= gate[T, H] in place (one gate per token and head); rows whose token_seq is negative are padding.
+template <typename TX>
+__global__ void head_gate_kernel(TX* __restrict__ x, const float* __restrict__ gate, const int* __restrict__ token_seq,
+                                 int H, int d, size_t total) {
+    pdl_enter(TR_GLU);
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t th = idx / d;
+        if (token_seq[th / H] < 0) continue;
+        x[idx] = from_float<TX>(to_float(x[idx]) * gate[th]);
     }
 }
 
@@ -66,6 +79,16 @@ AIR_API int air_glu(const void* in, int in_dtype, void* out, int out_dtype, int 
         return air::launch(air::glu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, (TO*)out, I, block, total,
                            alpha, limit, shift);
     }));
+    return 0;
+}
+
+AIR_API int air_head_gate(void* x, int dtype, const float* gate, const int* token_seq, int T, int H, int d,
+                          cudaStream_t stream) {
+    const size_t total = (size_t)T * H * d;
+    if (total == 0) return 0;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    AIR_DISPATCH(dtype, TX, return air::launch(air::head_gate_kernel<TX>, blocks, 256, 0, stream, (TX*)x, gate, token_seq,
+                                               H, d, total));
     return 0;
 }
 

@@ -51,14 +51,15 @@ _SIGNATURES = {
     "air_gemm_tc_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                           c_void_p, c_int, c_float, c_void_p],
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                  c_void_p],
+    "air_head_gate": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "air_decode_attention_tma_fresh": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     "air_prefill_attention_tc": [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                  c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                 c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                                 c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
     "air_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                    c_void_p, c_void_p],
 }
@@ -476,6 +477,17 @@ def gated_rmsnorm(o, gate, weight, eps, out, token_seq):
     return out
 
 
+def head_gate(x, gate, token_seq):
+    """x[t, h, :] *= gate[t, h] in place.  x [T, H, d]; gate float32 [T, H]."""
+    T, H, d = x.shape
+    _req(x, "x", _FLOATS)
+    _req(gate, "gate", (torch.float32,), (T, H))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _check(_get("air_head_gate")(x.data_ptr(), _DT[x.dtype], gate.data_ptr(), token_seq.data_ptr(), T, H, d, _stream()),
+           "head_gate")
+    return x
+
+
 def glu(gate_up, out, block=None, alpha=1.0, limit=0.0, shift=0.0):
     """out[t, i] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)
     where limit > 0; gate_up [T, 2I] as silu_mul takes it."""
@@ -570,8 +582,9 @@ def decode_splits(tokens: int, heads: int, kv_heads: int) -> int:
 
 
 def decode_attention(q, cache, block_table, token_seq, positions, out, window, scale, splits=None, scratch=None,
-                     status=None, engine="tma"):
-    """bfloat16 attention for one query token per request.  scratch: (float32 [T*H*splits*D], float32
+                     status=None, engine="tma", softcap=0.0):
+    """bfloat16 attention for one query token per request.  softcap > 0: score = softcap * tanh(scale * q.k /
+    softcap) (the copy-engine kernel only).  scratch: (float32 [T*H*splits*D], float32
     [T*H*splits*2]) or None to allocate.  engine "tma": keys and values by the copy engine into shared
     memory (attention_decode_tma.cu); "ldg": by the warps' own loads (attention_decode.cu)."""
     T, H, d = q.shape
@@ -601,7 +614,11 @@ def decode_attention(q, cache, block_table, token_seq, positions, out, window, s
         _check(_get("air_decode_attention_tma")(
             q.data_ptr(), cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
             token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(po), _ptr(pm), T, H, K, d, P,
-            int(window or 0), float(scale), splits, _ptr(status), _stream()), "decode_attention_tma")
+            int(window or 0), float(scale), float(softcap or 0.0), splits, _ptr(status), _stream()),
+            "decode_attention_tma")
+    elif softcap:
+        raise KernelError("decode_attention: a soft cap is taken by the copy-engine kernel only (pages that divide "
+                          "or are multiples of 64 tokens)")
     else:
         _check(_get("air_decode_attention")(
             q.data_ptr(), cache.data_ptr(), block_table.data_ptr(), block_table.shape[1], token_seq.data_ptr(),
@@ -753,9 +770,10 @@ def prefill_attention_scratch(slots: int, head_dim: int, device):
 
 
 def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, status=None, segments=None, items=None,
-                         slots=0, scratch=None):
+                         slots=0, scratch=None, softcap=0.0):
     """bfloat16 causal attention with both products on the tcgen05 tensor cores (see
-    attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128.
+    attention_prefill_tc.cu); arguments as prefill_attention; head size 64 or 128.  softcap > 0: score = softcap *
+    tanh(scale * q.k / softcap).
     segments [n, 5] int32 (pair of the list, head, first key tile, key tiles, slot or -1): which block takes which
     part of which pair's stream of keys, instead of one block per pair and head; items [m, 4] int32 (pair, head,
     first slot, slots): the (pair, head)s whose segments write partial sums into `slots` slots, merged here.
@@ -791,5 +809,6 @@ def prefill_attention_tc(q, cache, block_table, tiles, out, window, scale, statu
         q.data_ptr(), T, cache.data_ptr(), cache.shape[0], block_table.data_ptr(), block_table.shape[1],
         tiles.data_ptr(), tiles.shape[0], _ptr(segments), 0 if segments is None else segments.shape[0],
         _ptr(items) if n_items else None, n_items, int(slots) if segments is not None else 0, _ptr(part_o), _ptr(part_ml),
-        out.data_ptr(), H, K, d, P, int(window or 0), float(scale), _ptr(status), _stream()), "prefill_attention_tc")
+        out.data_ptr(), H, K, d, P, int(window or 0), float(scale), float(softcap or 0.0), _ptr(status), _stream()),
+        "prefill_attention_tc")
     return out

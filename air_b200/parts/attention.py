@@ -88,42 +88,12 @@ def plan_segments(key_tiles, heads: int, sms: int = 0):
     return segments, items, int(is_cut.sum())
 
 
-@register_mixer("attention")
-class Attention(Mixer):
-    """q, k, v projections (with optional biases), position encoding of q and k, causal
-    softmax attention with scale 1/sqrt(head_dim) in which query head h reads kv head
-    floor(h * kv_heads / heads), output projection
-    (AIR: src/reference/reference_executor.cpp:74-138, 349-384).
+class TiledAttention:
+    """What mixers that attend over paged keys and values of one size (PagedKV pages [2, K, P, d]) share: the plan of
+    a step's tiles, worked out on the host once for all such layers, and the choice of the attention kernel.  The
+    mixer has `heads`, `window`, `head_dim`, `scale`, `rt`, and `softcap` (0: none)."""
 
-    params: hidden, heads, kv_heads, head_dim, qkv_bias, window (None: all keys),
-            position (a PartSpec of a position encoding).
-    Tensors: <prefix>{q,k,v}_proj.weight [heads*d | kv*d, hidden], <prefix>{q,k,v}_proj.bias
-    (absent tensors mean no bias, as in AIR: src/model/qwen2_contract.cpp:133-136),
-    <prefix>o_proj.weight [hidden, heads*d].
-
-    At load the three projections become one matrix [(heads + 2 kv) d, hidden].  One kernel
-    then adds the bias, rotates q and k and writes k and v into the request's pages; the
-    attention kernel reads keys and values only from the pages, for prompt portions and
-    decoded tokens alike."""
-
-    graph_safe = True
-
-    def __init__(self, spec, prefix=""):
-        super().__init__(spec, prefix)
-        p = spec.params
-        self.hidden, self.heads, self.kv_heads, self.head_dim = p["hidden"], p["heads"], p["kv_heads"], p["head_dim"]
-        self.window = p.get("window")
-        self.qkv_bias = bool(p.get("qkv_bias", False))
-        if self.heads % self.kv_heads:
-            raise ConfigError("data_error", "attention: heads must be a multiple of kv_heads")
-        if self.head_dim % 16 or self.head_dim > 256:
-            raise ConfigError("unsupported", f"attention: head size {self.head_dim} is not a multiple of 16 up to "
-                                             "256, which is what the attention kernels take")
-        pos = p["position"]
-        self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
-
-    def cache_needs(self):
-        return (PagedKV(self.kv_heads, self.head_dim, self.window),)
+    softcap = 0.0
 
     # ------------------------------------------------------------------ the step's plan
     PLAN = "attention.tiles"
@@ -164,6 +134,86 @@ class Attention(Mixer):
             arrays["segments"], arrays["items"], values["slots"] = cut
             del values["segments"], values["items"]
         return Plan(arrays=arrays, values=values)
+
+    def fast_attention(self, ctx, page_tokens: int) -> bool:
+        """Whether this step's attention runs on the tensor-core kernels (bfloat16, a head size and a page size that
+        they take); else the 32-bit kernel computes it."""
+        d = self.head_dim
+        if self.rt.dtype != torch.bfloat16 or d not in ops.DECODE_HEAD_DIMS:
+            return False
+        if ctx.all_decode:
+            return not self.softcap or ops.tile_pages(page_tokens)
+        if self.plan_key() not in ctx.plans or not ops.tile_pages(page_tokens):
+            return False
+        return not self.softcap or d in ops.TC_ATTENTION_HEAD_DIMS
+
+    def attend(self, q, kv, bt, ctx, out):
+        """out [T, H, d] = causal attention of q [T, H, d] over the pages kv [pages, 2, K, P, d]."""
+        d = self.head_dim
+        if not self.fast_attention(ctx, kv.shape[3]):
+            return ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale,
+                                           softcap=self.softcap)
+        if ctx.all_decode:
+            return ops.decode_attention(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale,
+                                        softcap=self.softcap)
+        # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
+        # tile of 128 queries for one token would read its request's whole context for one row), the
+        # prompt portions the tile kernels
+        plan = ctx.plans[self.plan_key()]
+        n = plan.decode_prefix
+        if n:
+            ops.decode_attention(q[:n], kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window,
+                                 self.scale, softcap=self.softcap)
+        if plan.tiles.shape[0] == 0:
+            pass
+        elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
+            if plan.slots and getattr(plan, "scratch", None) is None:
+                # (the step's layers run one after the other on one stream and share the partial sums' memory)
+                plan.scratch = ops.prefill_attention_scratch(plan.slots, d, q.device)
+            ops.prefill_attention_tc(q, kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status,
+                                     segments=plan.segments, items=plan.items, slots=plan.slots,
+                                     scratch=getattr(plan, "scratch", None), softcap=self.softcap)
+        else:
+            ops.prefill_attention(q, kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
+        return out
+
+
+@register_mixer("attention")
+class Attention(TiledAttention, Mixer):
+    """q, k, v projections (with optional biases), position encoding of q and k, causal
+    softmax attention with scale 1/sqrt(head_dim) in which query head h reads kv head
+    floor(h * kv_heads / heads), output projection
+    (AIR: src/reference/reference_executor.cpp:74-138, 349-384).
+
+    params: hidden, heads, kv_heads, head_dim, qkv_bias, window (None: all keys),
+            position (a PartSpec of a position encoding).
+    Tensors: <prefix>{q,k,v}_proj.weight [heads*d | kv*d, hidden], <prefix>{q,k,v}_proj.bias
+    (absent tensors mean no bias, as in AIR: src/model/qwen2_contract.cpp:133-136),
+    <prefix>o_proj.weight [hidden, heads*d].
+
+    At load the three projections become one matrix [(heads + 2 kv) d, hidden].  One kernel
+    then adds the bias, rotates q and k and writes k and v into the request's pages; the
+    attention kernel reads keys and values only from the pages, for prompt portions and
+    decoded tokens alike."""
+
+    graph_safe = True
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.heads, self.kv_heads, self.head_dim = p["hidden"], p["heads"], p["kv_heads"], p["head_dim"]
+        self.window = p.get("window")
+        self.qkv_bias = bool(p.get("qkv_bias", False))
+        if self.heads % self.kv_heads:
+            raise ConfigError("data_error", "attention: heads must be a multiple of kv_heads")
+        if self.head_dim % 16 or self.head_dim > 256:
+            raise ConfigError("unsupported", f"attention: head size {self.head_dim} is not a multiple of 16 up to "
+                                             "256, which is what the attention kernels take")
+        pos = p["position"]
+        self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
+
+    def cache_needs(self):
+        return (PagedKV(self.kv_heads, self.head_dim, self.window),)
 
     def tensor_specs(self):
         d, p = self.head_dim, self.prefix
@@ -236,31 +286,7 @@ class Attention(Mixer):
         ops.qkv_rope_store(qkv, self.bias, table, ctx.positions, ctx.token_seq, bt, q, pages.kv,
                            H, K, d, write_kv=owns_cache, status=ctx.status)
         out = torch.empty_like(q)
-        if rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and ctx.all_decode:
-            ops.decode_attention(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
-        elif (rt.dtype == torch.bfloat16 and d in ops.DECODE_HEAD_DIMS and self.plan_key() in ctx.plans
-              and ops.tile_pages(pages.kv.shape[3])):
-            # a mixed step: the single next tokens at the head of the batch take the decode kernel (a row
-            # tile of 128 queries for one token would read its request's whole context for one row), the
-            # prompt portions the tile kernels
-            plan = ctx.plans[self.plan_key()]
-            n = plan.decode_prefix
-            if n:
-                ops.decode_attention(q[:n], pages.kv, bt, ctx.token_seq[:n], ctx.positions[:n], out[:n], self.window,
-                                     self.scale)
-            if plan.tiles.shape[0] == 0:
-                pass
-            elif d in ops.TC_ATTENTION_HEAD_DIMS:     # both products on the tcgen05 tensor cores
-                if plan.slots and getattr(plan, "scratch", None) is None:
-                    # (the step's layers run one after the other on one stream and share the partial sums' memory)
-                    plan.scratch = ops.prefill_attention_scratch(plan.slots, d, q.device)
-                ops.prefill_attention_tc(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status,
-                                         segments=plan.segments, items=plan.items, slots=plan.slots,
-                                         scratch=getattr(plan, "scratch", None))
-            else:
-                ops.prefill_attention(q, pages.kv, bt, plan.tiles, out, self.window, self.scale, status=ctx.status)
-        else:
-            ops.paged_attention_ref(q, pages.kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale)
+        self.attend(q, pages.kv, bt, ctx, out)
         return self._project(out.view(T, H * d), ctx)
 
     def _project(self, out, ctx):

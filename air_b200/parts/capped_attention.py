@@ -6,13 +6,14 @@ import torch
 from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
+from .attention import TiledAttention
 from .base import Mixer, PagedKV
 from .linear import Linear
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
 @register_mixer("capped_attention")
-class CappedAttention(Mixer):
+class CappedAttention(TiledAttention, Mixer):
     """Causal softmax attention over the paged cache in which
 
       * keys and queries have one size per head (head_dim) and values another (v_dim);
@@ -31,7 +32,9 @@ class CappedAttention(Mixer):
     <name>.b where qkv_bias; g [heads, hidden] where head_gate; vmix [] where v_mix; o [hidden, heads*v_dim].
 
     q, k, v and the gate are one product.  One kernel then adds the bias, rotates, mixes the values, writes keys and
-    values to the pages and the gates to a small tensor; the attention kernel multiplies by them as it writes."""
+    values to the pages and the gates to a small tensor.  In bfloat16, with keys and values of one size that the
+    tensor-core attention kernels take (64 or 128; 256 for single tokens), those kernels attend, with the cap in their
+    softmax, and a small kernel multiplies by the gates; otherwise the 32-bit attention kernel does all of it."""
 
     graph_safe = True
 
@@ -56,6 +59,10 @@ class CappedAttention(Mixer):
 
     def cache_needs(self):
         return (PagedKV(self.kv_heads, self.head_dim, self.window, self.v_dim),)
+
+    def plan_key(self):
+        # (the tile kernels take keys and values of one size: other layers plan nothing)
+        return TiledAttention.plan_key(self) if self.head_dim == self.v_dim else None
 
     def _names(self):
         return ["q", "k", "v"] + (["g"] if self.head_gate else [])
@@ -114,6 +121,11 @@ class CappedAttention(Mixer):
         ops.qkv_prepare(proj, self.bias, self.position.frequencies(), ctx.positions, ctx.token_seq, bt, q, kv, G, dv,
                         P, gate_out=gate, v_first=v_first, v_mode=v_mode, v_lambda=self.v_lambda, status=ctx.status)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
-        ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale,
-                                softcap=self.softcap, gate=gate, kv_heads=G, page_tokens=P)
+        if dk == dv and self.fast_attention(ctx, P):
+            self.attend(q, pages.kv, bt, ctx, out)
+            if gate is not None:
+                ops.head_gate(out, gate, ctx.token_seq)
+        else:
+            ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale,
+                                    softcap=self.softcap, gate=gate, kv_heads=G, page_tokens=P)
         return self.o.f32(out.view(T, H * dv))

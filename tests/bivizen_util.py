@@ -56,7 +56,7 @@ CONFIGS = {
         with_mlp(attention(2, 1, 64, 64, 0.125, softcap=4.0, rot=(32, 10000.0), v_mix=True), 128, 2.5),
         with_mlp(attention(1, 1, 128, 128, 0.09, softcap=3.0, rot=(128, 1e5)), 128, 2.5)]),
     "S": config(150, 96, 2e-6, [
-        with_mlp(attention(3, 3, 32, 32, 0.18, v_mix=True), 64, 1.0),
+        with_mlp(attention(3, 3, 24, 24, 0.18, v_mix=True), 64, 1.0),
         with_mlp(delta(3, 3, 32, 32, 1), 64, 1.0),
         with_mlp(gla(3, 16, 16, 1.0, 16), 64, 1.0)]),
 }
