@@ -15,7 +15,7 @@
 namespace air {
 
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qkv_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ bias,
                    const float* __restrict__ inv_freq, int rot, const int* __restrict__ positions,
                    const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
@@ -89,7 +89,7 @@ AIR_API int air_qkv_prepare(const float* proj, int ld, const float* bias, const 
     if (rot < 0 || rot > dk || (rot & 1) || (rot > 0 && !inv_freq) || v_mode < 0 || v_mode > 2 ||
         (v_mode && !v_first) || (v_mode == 2 && !lambda))
         return AIR_ERR_BAD_ARGUMENT;
-    AIR_DISPATCH(out_dtype, TO, return air::launch(air::qkv_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, bias,
+    AIR_DISPATCH(out_dtype, TO, return air::launch(air::qkv_prepare_kernel<TO>, T, T <= 64 ? 1024 : 256, 0, stream, proj, ld, bias,
                                                    inv_freq, rot, positions, token_seq, block_table, max_blocks,
                                                    (TO*)q_out, (TO*)cache, gate_out, v_first, v_mode, lambda, H, G, dk,
                                                    dv, P, status));

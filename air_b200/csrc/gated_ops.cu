@@ -96,7 +96,9 @@ AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, const flo
                             int w_dtype, void* out, int out_dtype, const int* rows, int R, int E, float eps,
                             cudaStream_t stream) {
     if (R <= 0) return 0;
-    const int threads = E >= 1024 ? 256 : 128;
+    // few rows: a block as wide as half a row, so that a row's loads are all under way at once
+    int threads = E >= 1024 ? 256 : 128;
+    if (R <= 256) threads = E / 2 >= 1024 ? 1024 : (E / 2 > threads ? (E / 2 + 31) / 32 * 32 : threads);
     const size_t smem = sizeof(float) * (size_t)E;
     if (smem > 200 * 1024) return AIR_ERR_BAD_ARGUMENT;
     AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {

@@ -48,6 +48,9 @@ struct TcArgs {
     int splits;         // parts of the k range (1 unless EPI_PARTIAL)
     int prefetch;       // further k-tiles of W that a block asks into L2 before its predecessor has ended
     int* status;
+    // EPI_SILU computes g' * sigmoid(act_alpha * g') * (u' + act_shift) with g' = min(gate, act_limit) and
+    // u' = clamp(up, -act_limit, act_limit) where act_limit > 0: (1, 0, 0) is SiLU(gate) * up.
+    float act_alpha, act_limit, act_shift;
 };
 
 // Stages of the ring for a tile width and a height of A's box: what fits in 196 KB, at most 24.
@@ -235,8 +238,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 float y[8];
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) {
-                                    const float g = __uint_as_float(gate[j + e]), u = __uint_as_float(up[j + e]);
-                                    y[e] = g / (1.f + expf(-g)) * u;
+                                    float g = __uint_as_float(gate[j + e]), u = __uint_as_float(up[j + e]);
+                                    if (args.act_limit > 0.f) {
+                                        g = fminf(g, args.act_limit);
+                                        u = fminf(fmaxf(u, -args.act_limit), args.act_limit);
+                                    }
+                                    y[e] = g / (1.f + expf(-args.act_alpha * g)) * (u + args.act_shift);
                                 }
                                 store4(out + c + j, *(const float(*)[4])&y[0]);
                                 store4(out + c + j + 4, *(const float(*)[4])&y[4]);
@@ -343,9 +350,11 @@ static int dispatch_rows(int a_rows, int epi, const CUtensorMap& ma, const CUten
 }  // namespace air
 
 // a [M, K] bf16, w [N, K] bf16 (for epi 2: gate and up rows interleaved in blocks of bn / 2), K % 8 == 0.
-// out as TcArgs.out.  bn: 32, 64, 128 or 256.  max_blocks: the number of SMs to use (0: all).
+// out as TcArgs.out.  bn: 32, 64, 128 or 256.  max_blocks: the number of SMs to use (0: all).  act_*: the gated
+// activation of epi 2 (TcArgs).
 AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, int K, int bn, int epi, int splits,
-                        int max_blocks, int* status, cudaStream_t stream) {
+                        int max_blocks, int* status, float act_alpha, float act_limit, float act_shift,
+                        cudaStream_t stream) {
     using namespace air;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || splits < 1 || (splits > 1 && epi != EPI_PARTIAL) || ((uintptr_t)a & 15) ||
@@ -375,7 +384,7 @@ AIR_API int air_gemm_tc(const void* a, const void* w, void* out, int M, int N, i
     // With few rows the product is a stream of weights: while the predecessor runs, each block asks
     // its share of up to 40 MB of them into L2 (the L2 holds 126 MB).
     const int prefetch = M <= 64 ? (int)((40ll << 20) / blocks / (bn * TC_BK * 2)) : 0;
-    TcArgs args{out, M, N, K, a_rows, splits, prefetch, status};
+    TcArgs args{out, M, N, K, a_rows, splits, prefetch, status, act_alpha, act_limit, act_shift};
     switch (bn) {
         case 32: return dispatch_rows<32>(a_rows, epi, ma, mw, args, blocks, stream);
         case 64: return dispatch_rows<64>(a_rows, epi, ma, mw, args, blocks, stream);

@@ -42,6 +42,9 @@ struct TsArgs {
     const float* ss;
     int ss_tiles;
     float eps;
+    // SILU computes g' * sigmoid(act_alpha * g') * (u' + act_shift) with g' = min(gate, act_limit) and
+    // u' = clamp(up, -act_limit, act_limit) where act_limit > 0: (1, 0, 0) is SiLU(gate) * up.
+    float act_alpha, act_limit, act_shift;
 };
 
 __host__ __device__ constexpr int ts_stages(int nt, int halves) {
@@ -241,8 +244,15 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     __nv_bfloat16* out = (__nv_bfloat16*)args.out + col;
 #pragma unroll
                     for (int t = 0; t < NT; ++t)
-                        if (t < args.T)
-                            out[(size_t)t * (args.N / 2)] = __float2bfloat16_rn(gate[t] / (1.f + expf(-gate[t])) * up[t]);
+                        if (t < args.T) {
+                            float g = gate[t], u = up[t];
+                            if (args.act_limit > 0.f) {
+                                g = fminf(g, args.act_limit);
+                                u = fminf(fmaxf(u, -args.act_limit), args.act_limit);
+                            }
+                            out[(size_t)t * (args.N / 2)] =
+                                __float2bfloat16_rn(g / (1.f + expf(-args.act_alpha * g)) * (u + args.act_shift));
+                        }
                 }
             } else {
 #pragma unroll
@@ -339,7 +349,7 @@ static int ts_dispatch_tokens(int nt, int epi, const CUtensorMap& mw, const CUte
 // SMs to use (0: all).
 AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, int N, int K, int tile_rows, int epi,
                               int splits, int max_blocks, int* status, const float* ss, int ss_tiles, float eps,
-                              cudaStream_t stream) {
+                              float act_alpha, float act_limit, float act_shift, cudaStream_t stream) {
     using namespace air;
     if (T <= 0 || N <= 0) return 0;
     if (T > 64 || K <= 0 || K % 8 || splits < 1 || (splits > 1 && epi != TS_PARTIAL) || ((uintptr_t)x & 15) ||
@@ -363,7 +373,7 @@ AIR_API int air_gemm_tc_small(const void* x, const void* w, void* out, int T, in
     const long long tiles = (long long)((N + tile_rows - 1) / tile_rows) * splits;
     const int blocks = (int)(tiles < sms ? tiles : sms);
     if (ss && ss_tiles < 1) return AIR_ERR_BAD_ARGUMENT;
-    TsArgs args{out, T, N, K, splits, status, ss, ss_tiles, eps};
+    TsArgs args{out, T, N, K, splits, status, ss, ss_tiles, eps, act_alpha, act_limit, act_shift};
     if (tile_rows == 256) return ts_dispatch_tokens<2>(nt, epi, mw, mx, args, blocks, stream);
     return ts_dispatch_tokens<1>(nt, epi, mw, mx, args, blocks, stream);
 }

@@ -35,8 +35,8 @@ _SIGNATURES = {
     "air_short_conv_silu": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                             c_int, c_void_p],
     "air_linear_scan": [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
-                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                        c_float, c_float, c_int, c_float, c_void_p],
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_float, c_void_p],
     "air_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
                           c_void_p],
     "air_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
@@ -47,9 +47,10 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "air_prefill_attention": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                               c_int, c_int, c_int, c_float, c_void_p, c_void_p],
-    "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "air_gemm_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+                    c_float, c_float, c_void_p],
     "air_gemm_tc_small": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                          c_void_p, c_int, c_float, c_void_p],
+                          c_void_p, c_int, c_float, c_float, c_float, c_float, c_void_p],
     "air_decode_attention_tma": [c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                  c_void_p],
@@ -415,11 +416,13 @@ def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
 SCAN_DELTA, SCAN_GLA = 0, 1
 
 
-def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, q_scale=1.0, beta=None, a_log=None, dt_bias=None,
-                tau=1.0, unit=False, unit_eps=1e-6):
+def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, token_seq, q_scale=1.0, beta=None, a_log=None,
+                dt_bias=None, tau=1.0, unit=False, unit_eps=1e-6):
     """A state S [d, dv] per head and request, updated token by token in 32-bit and read out after each update.
     q, k float32 [T, G * d], v [T, H * dv] (each may be a band of columns of a wider matrix); head h reads q/k head
-    h // (H / G); state [slots, H, d, dv]; out [T, H, dv].
+    h // (H / G); state [slots, H, d, dv]; out [T, H, dv]; token_seq [T]: the slot of each row's request (negative:
+    padding).  Two launches: what the recurrence reads per token (unit lengths, scales, decays) is worked out for all
+    tokens side by side, then the scan takes the tokens of each request in order.
     SCAN_DELTA: decay, beta [T, H] logits; g = exp(-exp(a_log[h]) * softplus(decay + dt_bias[h])), b = sigmoid(beta);
       with unit, q and k are first divided by sqrt(sum of squares + unit_eps), q then multiplied by q_scale;
       S = g S; u = b (v - S^T k); S += k u^T; o = S^T q.
@@ -454,10 +457,20 @@ def linear_scan(mode, q, k, v, decay, state, out, q_start, slots, q_scale=1.0, b
         raise KernelError(f"linear_scan: {d} key channels per head (the kernel takes up to 1,024)")
     _req(q_start, "q_start", _I32)
     _req(slots, "slots", _I32)
+    _req(token_seq, "token_seq", _I32, (T,))
+    rows = 16 if d <= 512 else 32          # of a column of the state per lane; lanes per column: a power of two
+    lanes = 1
+    while lanes * rows < d:
+        lanes *= 2
+    kq = torch.empty((T, G, 2, lanes * rows), dtype=torch.float32, device=out.device)
+    dec = torch.empty((T, H, 2 if mode == SCAN_DELTA else lanes * rows), dtype=torch.float32, device=out.device)
     _check(_get("air_linear_scan")(
         int(mode), qp, ldq, kp, ldk, vp, ldv, dp, ldd, bp, ldb, _ptr(a_log), _ptr(dt_bias), state.data_ptr(),
-        out.data_ptr(), q_start.data_ptr(), slots.data_ptr(), slots.shape[0], H, G, d, dv, float(q_scale),
-        1.0 / float(tau), 1 if unit else 0, float(unit_eps), _stream()), "linear_scan")
+        out.data_ptr(), q_start.data_ptr(), slots.data_ptr(), token_seq.data_ptr(), kq.data_ptr(), dec.data_ptr(),
+        T, slots.shape[0], H, G, d, dv, lanes, float(q_scale), 1.0 / float(tau), 1 if unit else 0, float(unit_eps),
+        _stream()), "linear_scan")
+    global launches
+    launches += 1
     return out
 
 
@@ -705,13 +718,19 @@ def prefill_attention(q, cache, block_table, tiles, out, window, scale, status=N
 EPI_F32, EPI_BF16, EPI_SILU, EPI_PARTIAL = 0, 1, 2, 3
 
 
-def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_as_m=False, row_ss=None, eps=0.0):
+SILU = (1.0, 0.0, 0.0)      # the gated activation of EPI_SILU as (alpha, limit, shift): see gemm_tc
+
+
+def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_as_m=False, row_ss=None, eps=0.0,
+            act=SILU):
     """bfloat16 product a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (see gemm_tc.cu).
     row_ss (float32 [tiles, M]) with eps: the accumulators are multiplied per row by
     rsqrt(sum over tiles of row_ss / K + eps) before the epilogue (the kernel for few rows only; see
     add_prenorm).
     epi EPI_F32: out float32 [M,N]; EPI_BF16: out bfloat16 [M,N]; EPI_SILU: w holds gate and up rows
-    interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up; EPI_PARTIAL: out float32
+    interleaved in blocks of bn/2, out bfloat16 [M,N/2] = silu(gate)*up, or with act = (alpha, limit, shift)
+    g * sigmoid(alpha * g) * (u + shift) where g = min(gate, limit), u = clamp(up, -limit, limit) if limit > 0;
+    EPI_PARTIAL: out float32
     [splits,M,N] partial sums over parts of k.  With up to 64 rows and bn 128 or 256 the product runs with the
     weights as the M side of the instruction (gemm_tc_small.cu) unless force_rows_as_m."""
     M, K = a.shape
@@ -742,13 +761,14 @@ def gemm_tc(a, w, out, bn, epi, splits=1, status=None, max_blocks=0, force_rows_
         # few tokens: the weights are the M side of the instruction (gemm_tc_small.cu)
         _check(_get("air_gemm_tc_small")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits,
                                          max_blocks, _ptr(status), _ptr(row_ss),
-                                         0 if row_ss is None else row_ss.shape[0], float(eps), _stream()),
+                                         0 if row_ss is None else row_ss.shape[0], float(eps), float(act[0]),
+                                         float(act[1]), float(act[2]), _stream()),
                "gemm_tc_small")
         return out
     if row_ss is not None:
         raise KernelError("gemm_tc: a scale per row is taken by the kernel for up to 64 rows only")
     _check(_get("air_gemm_tc")(a.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K, bn, epi, splits, max_blocks,
-                               _ptr(status), _stream()), "gemm_tc")
+                               _ptr(status), float(act[0]), float(act[1]), float(act[2]), _stream()), "gemm_tc")
     return out
 
 

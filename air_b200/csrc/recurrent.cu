@@ -5,6 +5,7 @@
 //
 //   short_conv_silu_kernel   y[t, c] = silu(sum_j w[c, j] x[t - (taps - 1 - j), c]): a causal convolution over time
 //                            per channel whose last taps - 1 inputs are the state (zeros before a request's start)
+//   scan_prepare_kernel      what a scan reads per token (unit lengths, scales, decays), for all tokens side by side
 //   linear_scan_kernel       a state S [d, dv] per head, updated token by token, read out after each update:
 //                              DELTA  S = g S;  u = beta (v - S^T k);  S += k u^T;  o = S^T q   (one decay per head)
 //                              GLA    S = diag(alpha) S + k v^T;  o = S^T q                      (a decay per key channel)
@@ -85,30 +86,98 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restr
 
 enum { SCAN_DELTA = 0, SCAN_GLA = 1 };
 constexpr int SCAN_THREADS = 128;
-constexpr int SCAN_TOKENS = 16;      // tokens staged in shared memory at a time
 
-struct ScanArgs {
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// What the scan reads per token, worked out for all tokens side by side (one block per token and head of q and k):
+//   kq [T, G, 2, dpad]   k and then q of the head, as the recurrence takes them (unit length and q's scale for the
+//                        delta rule, q's scale for gated linear attention), zeros from d to dpad
+//   dec                  DELTA [T, H, 2]: g = exp(-exp(a_log) softplus(decay + dt_bias)) and b = sigmoid(beta)
+//                        GLA   [T, H, dpad]: alpha = sigmoid(decay)^(1 / tau) per key channel, zeros from d on
+struct ScanPrepArgs {
     const float* q; int ldq;         // [T, ldq]: head g's d elements at column g * d
     const float* k; int ldk;
-    const float* v; int ldv;         // head h's dv elements at column h * dv
     const float* decay; int ldd;     // DELTA: [T, ldd] one logit per head;  GLA: [T, ldd] d logits per head
     const float* beta; int ldb;      // DELTA: [T, ldb] one logit per head
     const float* a_log;              // DELTA: [H]
     const float* dt_bias;            // DELTA: [H]
+    const int* token_seq;
+    float* kq;
+    float* dec;
+    int H, G, d, dpad;
+    float q_scale, inv_tau, unit_eps;
+    int unit;                        // q and k are divided by sqrt(sum of squares + unit_eps) first
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(128) scan_prepare_kernel(const ScanPrepArgs p) {
+    __shared__ float scratch[32];
+    pdl_enter(TR_SCAN);
+    const int t = blockIdx.x, g = blockIdx.y;
+    if (p.token_seq[t] < 0) return;
+    const float* kin = p.k + (size_t)t * p.ldk + g * p.d;
+    const float* qin = p.q + (size_t)t * p.ldq + g * p.d;
+    float kf = 1.f, qf = p.q_scale;
+    if (p.unit) {
+        float sk = 0.f, sq = 0.f;
+        for (int r = threadIdx.x; r < p.d; r += blockDim.x) {
+            sk = fmaf(kin[r], kin[r], sk);
+            sq = fmaf(qin[r], qin[r], sq);
+        }
+        kf = 1.f / sqrtf(block_sum(sk, scratch) + p.unit_eps);
+        qf = p.q_scale / sqrtf(block_sum(sq, scratch) + p.unit_eps);
+    }
+    float* out = p.kq + ((size_t)t * p.G + g) * 2 * p.dpad;
+    for (int r = threadIdx.x; r < p.dpad; r += blockDim.x) {
+        out[r] = r < p.d ? kin[r] * kf : 0.f;
+        out[p.dpad + r] = r < p.d ? qin[r] * qf : 0.f;
+    }
+    if (MODE == SCAN_GLA) {
+        const float* z = p.decay + (size_t)t * p.ldd + g * p.d;
+        float* a = p.dec + ((size_t)t * p.H + g) * p.dpad;
+        for (int r = threadIdx.x; r < p.dpad; r += blockDim.x)
+            a[r] = r < p.d ? expf(p.inv_tau * log_sigmoid_f(z[r])) : 0.f;
+    } else if (g == 0) {
+        for (int h = threadIdx.x; h < p.H; h += blockDim.x) {
+            p.dec[((size_t)t * p.H + h) * 2] =
+                expf(-expf(p.a_log[h]) * softplus_f(p.decay[(size_t)t * p.ldd + h] + p.dt_bias[h]));
+            p.dec[((size_t)t * p.H + h) * 2 + 1] = 1.f / (1.f + expf(-p.beta[(size_t)t * p.ldb + h]));
+        }
+    }
+}
+
+struct ScanArgs {
+    const float* kq;                 // [T, G, 2, dpad] (scan_prepare_kernel)
+    const float* dec;                // DELTA [T, H, 2];  GLA [T, H, dpad]
+    const float* v; int ldv;         // [T, ldv]: head h's dv elements at column h * dv
     float* state;                    // [slots, H, d, dv]
     float* out;                      // [T, H, dv]
     const int* q_start;
     const int* slots;
     int H, G, d, dv, L;              // G: heads of q and k (head h reads h / (H / G)); L lanes hold a column
-    float q_scale, inv_tau, unit_eps;
-    int unit;                        // q and k are divided by sqrt(sum of squares + unit_eps) first
+    int tokens;                      // tokens staged in shared memory at a time (two such buffers)
 };
 
-template <int MODE, int R>
+// The staging is a copy (cp.async) into one of two buffers: the next tokens arrive while these are computed.
+// A token's time is a chain of dependent instructions (decay, the sum over the column for the delta rule's
+// prediction, the update), so the chain is kept short: L and R are compile-time (unrolled loops, no address
+// arithmetic), and the read-out's sum over a column's lanes is not part of it: every lane leaves its partial sum
+// in shared memory and the sums are taken, in a fixed order, when a buffer's tokens are written out.
+template <int MODE, int R, int L>
 __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArgs p) {
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     pdl_enter(TR_SCAN);
-    const int L = p.L, cpw = 32 / L, CB = SCAN_THREADS / L, dpad = L * R;
+    constexpr int cpw = 32 / L, CB = SCAN_THREADS / L, dpad = L * R;
+    const int TK = p.tokens;
     const int e = blockIdx.z, h = blockIdx.y;
     const int slot = p.slots[e];
     if (slot < 0) return;
@@ -120,12 +189,39 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
     const bool live = col < p.dv;
     const int g = h / (p.H / p.G);
 
-    float* sk = smem;                                            // [SCAN_TOKENS][dpad]
-    float* sq = sk + SCAN_TOKENS * dpad;                         // [SCAN_TOKENS][dpad]
-    float* sa = sq + SCAN_TOKENS * dpad;                         // GLA: [SCAN_TOKENS][dpad];  DELTA: g, beta [2][SCAN_TOKENS]
-    float* sv = sa + (MODE == SCAN_GLA ? SCAN_TOKENS * dpad : 2 * SCAN_TOKENS);   // [SCAN_TOKENS][CB]
-    float* so = sv + SCAN_TOKENS * CB;                           // [SCAN_TOKENS][CB]
+    // a buffer: kq [TK][2][dpad], then (GLA) alpha [TK][dpad] or (DELTA) g, b [TK][2], then v [TK][CB]
+    const int dec_floats = MODE == SCAN_GLA ? TK * dpad : ((2 * TK + 3) & ~3);
+    const int buf_floats = TK * 2 * dpad + dec_floats + TK * CB;
+    float* so = smem + 2 * buf_floats;                           // [TK][CB][L]: the lanes' partial read-outs
 
+    auto stage = [&](int t0, int b) {
+        const int cnt = min(TK, n - t0);
+        float* bkq = smem + b * buf_floats;
+        float* bdec = bkq + TK * 2 * dpad;
+        float* bv = bdec + dec_floats;
+        constexpr int per_token = 2 * dpad / 4;
+        for (int idx = threadIdx.x; idx < cnt * per_token; idx += SCAN_THREADS) {
+            const int tt = idx / per_token, c = idx % per_token;
+            cp_async16(bkq + tt * 2 * dpad + 4 * c, p.kq + ((size_t)(q0 + t0 + tt) * p.G + g) * 2 * dpad + 4 * c);
+        }
+        if (MODE == SCAN_GLA) {
+            constexpr int per = dpad / 4;
+            for (int idx = threadIdx.x; idx < cnt * per; idx += SCAN_THREADS) {
+                const int tt = idx / per, c = idx % per;
+                cp_async16(bdec + tt * dpad + 4 * c, p.dec + ((size_t)(q0 + t0 + tt) * p.H + h) * dpad + 4 * c);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < cnt * 2; idx += SCAN_THREADS)
+                cp_async4(bdec + idx, p.dec + ((size_t)(q0 + t0 + idx / 2) * p.H + h) * 2 + (idx & 1));
+        }
+        for (int idx = threadIdx.x; idx < cnt * CB; idx += SCAN_THREADS) {
+            const int tt = idx / CB, c = blockIdx.x * CB + idx % CB;
+            if (c < p.dv) cp_async4(bv + idx, p.v + (size_t)(q0 + t0 + tt) * p.ldv + h * p.dv + c);
+        }
+        cp_async_commit();
+    };
+
+    stage(0, 0);
     float S[R];
     float* st = p.state + ((size_t)slot * p.H + h) * p.d * p.dv;
 #pragma unroll
@@ -133,95 +229,58 @@ __global__ void __launch_bounds__(SCAN_THREADS) linear_scan_kernel(const ScanArg
         const int r = i * L + l;
         S[i] = (live && r < p.d) ? st[(size_t)r * p.dv + col] : 0.f;
     }
-    float neg_a = 0.f, dtb = 0.f;
-    if (MODE == SCAN_DELTA) {
-        neg_a = -expf(p.a_log[h]);
-        dtb = p.dt_bias[h];
-    }
 
-    for (int t0 = 0; t0 < n; t0 += SCAN_TOKENS) {
-        const int cnt = min(SCAN_TOKENS, n - t0);
-        for (int idx = threadIdx.x; idx < SCAN_TOKENS * dpad; idx += SCAN_THREADS) {
-            const int tt = idx / dpad, r = idx % dpad;
-            float kv = 0.f, qv = 0.f, av = 1.f;
-            if (tt < cnt && r < p.d) {
-                const size_t row = (size_t)(q0 + t0 + tt);
-                kv = p.k[row * p.ldk + g * p.d + r];
-                qv = p.q[row * p.ldq + g * p.d + r];
-                if (MODE == SCAN_GLA) {
-                    qv *= p.q_scale;
-                    av = expf(p.inv_tau * log_sigmoid_f(p.decay[row * p.ldd + h * p.d + r]));
-                }
-            }
-            sk[idx] = kv;
-            sq[idx] = qv;
-            if (MODE == SCAN_GLA) sa[idx] = av;
-        }
-        for (int idx = threadIdx.x; idx < SCAN_TOKENS * CB; idx += SCAN_THREADS) {
-            const int tt = idx / CB, c = blockIdx.x * CB + idx % CB;
-            sv[idx] = (tt < cnt && c < p.dv) ? p.v[(size_t)(q0 + t0 + tt) * p.ldv + h * p.dv + c] : 0.f;
-        }
-        if (MODE == SCAN_DELTA && threadIdx.x < SCAN_TOKENS) {
-            const int tt = threadIdx.x;
-            float gv = 1.f, bv = 0.f;
-            if (tt < cnt) {
-                const size_t row = (size_t)(q0 + t0 + tt);
-                gv = expf(neg_a * softplus_f(p.decay[row * p.ldd + h] + dtb));
-                bv = 1.f / (1.f + expf(-p.beta[row * p.ldb + h]));
-            }
-            sa[tt] = gv;
-            sa[SCAN_TOKENS + tt] = bv;
-        }
-        __syncthreads();
-        if (p.unit) {
-            // q and k of every staged token to unit length (q also times q_scale): a warp per vector
-            for (int item = warp; item < 2 * cnt; item += SCAN_THREADS / 32) {
-                float* vec = (item & 1 ? sq : sk) + (item >> 1) * dpad;
-                float ss = 0.f;
-                for (int r = lane; r < p.d; r += 32) ss = fmaf(vec[r], vec[r], ss);
-                ss = warp_sum(ss);
-                const float f = (item & 1 ? p.q_scale : 1.f) / sqrtf(ss + p.unit_eps);
-                for (int r = lane; r < p.d; r += 32) vec[r] *= f;
-            }
-            __syncthreads();
-        }
+    int b = 0;
+    for (int t0 = 0; t0 < n; t0 += TK, b ^= 1) {
+        const int cnt = min(TK, n - t0);
+        cp_async_wait_all();
+        __syncthreads();                       // this buffer has landed; the other one and `so` are free again
+        if (t0 + TK < n) stage(t0 + TK, b ^ 1);
+        const float* bkq = smem + b * buf_floats;
+        const float* bdec = bkq + TK * 2 * dpad;
+        const float* bv = bdec + dec_floats;
         for (int tt = 0; tt < cnt; ++tt) {
-            const float* kk = sk + tt * dpad + l;
-            const float* qq = sq + tt * dpad + l;
-            const float vv = sv[tt * CB + cc];
-            float o = 0.f;
+            const float* kk = bkq + tt * 2 * dpad + l;
+            const float* qq = kk + dpad;
+            const float vv = live ? bv[tt * CB + cc] : 0.f;
+            // (four partial sums each: the chain of dependent additions is a quarter as long)
+            float orr[4] = {0.f, 0.f, 0.f, 0.f};
             if (MODE == SCAN_DELTA) {
-                const float gv = sa[tt], bv = sa[SCAN_TOKENS + tt];
-                float pred = 0.f;
+                const float gv = bdec[2 * tt], bb = bdec[2 * tt + 1];
+                float kr[R], pr[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
+                    kr[i] = kk[i * L];
                     S[i] *= gv;
-                    pred = fmaf(S[i], kk[i * L], pred);
+                    pr[i & 3] = fmaf(S[i], kr[i], pr[i & 3]);
                 }
+                float pred = (pr[0] + pr[1]) + (pr[2] + pr[3]);
+#pragma unroll
                 for (int off = 16; off >= cpw; off >>= 1) pred += __shfl_xor_sync(0xffffffffu, pred, off);
-                const float u = bv * (vv - pred);
+                const float u = bb * (vv - pred);
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
-                    S[i] = fmaf(kk[i * L], u, S[i]);
-                    o = fmaf(S[i], qq[i * L], o);
+                    S[i] = fmaf(kr[i], u, S[i]);
+                    orr[i & 3] = fmaf(S[i], qq[i * L], orr[i & 3]);
                 }
             } else {
-                const float* aa = sa + tt * dpad + l;
+                const float* aa = bdec + tt * dpad + l;
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
                     S[i] = fmaf(aa[i * L], S[i], kk[i * L] * vv);
-                    o = fmaf(S[i], qq[i * L], o);
+                    orr[i & 3] = fmaf(S[i], qq[i * L], orr[i & 3]);
                 }
             }
-            for (int off = 16; off >= cpw; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-            if (l == 0) so[tt * CB + cc] = o;
+            so[(tt * CB + cc) * L + l] = (orr[0] + orr[1]) + (orr[2] + orr[3]);
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < cnt * CB; idx += SCAN_THREADS) {
             const int tt = idx / CB, c = blockIdx.x * CB + idx % CB;
-            if (c < p.dv) p.out[((size_t)(q0 + t0 + tt) * p.H + h) * p.dv + c] = so[idx];
+            float o = 0.f;
+#pragma unroll
+            for (int j = 0; j < L; ++j) o += so[idx * L + j];
+            if (c < p.dv) p.out[((size_t)(q0 + t0 + tt) * p.H + h) * p.dv + c] = o;
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
@@ -251,28 +310,42 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ gate
         out[(size_t)item * dv + i] = from_float<TO>(row[i] * scale * w[i] * silu_f(gr[i]));
 }
 
+// rows of a column per lane: 16 up to 512 key channels, 32 beyond
+static int scan_rows(int d) { return d <= 512 ? 16 : 32; }
+
 template <int MODE>
-static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
-    // rows of a column per lane: 16 up to 512 key channels, 32 beyond; lanes per column: the power of two that covers d
-    const int R = a.d <= 512 ? 16 : 32;
-    int L = 1;
-    while (L * R < a.d) L *= 2;
-    if (L > 32) return AIR_ERR_BAD_ARGUMENT;
+static int launch_scan(const ScanPrepArgs& prep, const ScanArgs& a, int T, int S, cudaStream_t stream) {
+    const int R = scan_rows(a.d), L = a.L, dpad = L * R;
+    if (L < 1 || L > 32 || (L & (L - 1)) || dpad < a.d || prep.dpad != dpad || (R == 32 && L != 32))
+        return AIR_ERR_BAD_ARGUMENT;
+    if (a.H > 65535 || S > 65535 || prep.G > 65535) return AIR_ERR_BAD_ARGUMENT;
+    int rc = launch(scan_prepare_kernel<MODE>, dim3(T, prep.G), 128, 0, stream, prep);
+    if (rc) return rc;
     ScanArgs p = a;
-    p.L = L;
-    const int CB = SCAN_THREADS / L, dpad = L * R;
-    const size_t smem = sizeof(float) * ((size_t)SCAN_TOKENS * dpad * (MODE == SCAN_GLA ? 3 : 2) +
-                                         (MODE == SCAN_GLA ? 0 : 2 * SCAN_TOKENS) + 2 * (size_t)SCAN_TOKENS * CB);
-    dim3 grid((a.dv + CB - 1) / CB, a.H, S);
-    if (a.H > 65535 || S > 65535) return AIR_ERR_BAD_ARGUMENT;
-    if (R == 16) {
-        auto kernel = linear_scan_kernel<MODE, 16>;
+    const int CB = SCAN_THREADS / L;
+    // two buffers of `tokens` tokens each, and their partial read-outs, within 96 KB
+    auto bytes = [&](int tk) {
+        const size_t dec = MODE == SCAN_GLA ? (size_t)tk * dpad : (size_t)((2 * tk + 3) & ~3);
+        return sizeof(float) * (2 * ((size_t)tk * 2 * dpad + dec + (size_t)tk * CB) + (size_t)tk * SCAN_THREADS);
+    };
+    int tk = 16;
+    while (tk > 1 && bytes(tk) > 96 * 1024) tk /= 2;
+    p.tokens = tk;
+    const size_t smem = bytes(tk);
+    const dim3 grid((a.dv + CB - 1) / CB, a.H, S);
+    auto go = [&](auto kernel) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return launch(kernel, grid, SCAN_THREADS, smem, stream, p);
+    };
+    if (R == 32) return go(linear_scan_kernel<MODE, 32, 32>);
+    switch (L) {
+        case 1: return go(linear_scan_kernel<MODE, 16, 1>);
+        case 2: return go(linear_scan_kernel<MODE, 16, 2>);
+        case 4: return go(linear_scan_kernel<MODE, 16, 4>);
+        case 8: return go(linear_scan_kernel<MODE, 16, 8>);
+        case 16: return go(linear_scan_kernel<MODE, 16, 16>);
+        default: return go(linear_scan_kernel<MODE, 16, 32>);
     }
-    auto kernel = linear_scan_kernel<MODE, 32>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch(kernel, grid, SCAN_THREADS, smem, stream, p);
 }
 
 }  // namespace air
@@ -290,20 +363,26 @@ AIR_API int air_short_conv_silu(const float* x, int ld, const float* w, float* s
                        slots, C, taps, chunk);
 }
 
+// kq: float32 workspace [T, G, 2, L * R] and dec: [T, H, 2] (mode 0) or [T, H, L * R] (mode 1), with R = 16 up to
+// 512 key channels and 32 beyond, L the power of two with L * R >= d.
 AIR_API int air_linear_scan(int mode, const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
                             const float* decay, int ldd, const float* beta, int ldb, const float* a_log,
                             const float* dt_bias, float* state, float* out, const int* q_start, const int* slots,
-                            int S, int H, int G, int d, int dv, float q_scale, float inv_tau, int unit, float unit_eps,
-                            cudaStream_t stream) {
-    if (S <= 0) return 0;
-    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0) return AIR_ERR_BAD_ARGUMENT;
+                            const int* token_seq, float* kq, float* dec, int T, int S, int H, int G, int d, int dv,
+                            int L, float q_scale, float inv_tau, int unit, float unit_eps, cudaStream_t stream) {
+    if (S <= 0 || T <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || !kq || !dec || ((uintptr_t)kq & 15) || ((uintptr_t)dec & 15))
+        return AIR_ERR_BAD_ARGUMENT;
+    air::ScanPrepArgs pr;
+    pr.q = q; pr.ldq = ldq; pr.k = k; pr.ldk = ldk; pr.decay = decay; pr.ldd = ldd; pr.beta = beta; pr.ldb = ldb;
+    pr.a_log = a_log; pr.dt_bias = dt_bias; pr.token_seq = token_seq; pr.kq = kq; pr.dec = dec; pr.H = H; pr.G = G;
+    pr.d = d; pr.dpad = L * air::scan_rows(d); pr.q_scale = q_scale; pr.inv_tau = inv_tau; pr.unit_eps = unit_eps;
+    pr.unit = unit;
     air::ScanArgs a;
-    a.q = q; a.ldq = ldq; a.k = k; a.ldk = ldk; a.v = v; a.ldv = ldv; a.decay = decay; a.ldd = ldd;
-    a.beta = beta; a.ldb = ldb; a.a_log = a_log; a.dt_bias = dt_bias; a.state = state; a.out = out;
-    a.q_start = q_start; a.slots = slots; a.H = H; a.G = G; a.d = d; a.dv = dv; a.L = 0;
-    a.q_scale = q_scale; a.inv_tau = inv_tau; a.unit_eps = unit_eps; a.unit = unit;
-    if (mode == air::SCAN_DELTA) return air::launch_scan<air::SCAN_DELTA>(a, S, stream);
-    if (mode == air::SCAN_GLA) return air::launch_scan<air::SCAN_GLA>(a, S, stream);
+    a.kq = kq; a.dec = dec; a.v = v; a.ldv = ldv; a.state = state; a.out = out; a.q_start = q_start; a.slots = slots;
+    a.H = H; a.G = G; a.d = d; a.dv = dv; a.L = L; a.tokens = 0;
+    if (mode == air::SCAN_DELTA) return air::launch_scan<air::SCAN_DELTA>(pr, a, T, S, stream);
+    if (mode == air::SCAN_GLA) return air::launch_scan<air::SCAN_GLA>(pr, a, T, S, stream);
     return AIR_ERR_BAD_ARGUMENT;
 }
 

@@ -94,11 +94,13 @@ class Linear:
         out = torch.empty((x.shape[0], self.out_features), dtype=torch.float32, device=x.device)
         return ops.gemm_tc(x, self.weight, out, bn, ops.EPI_F32, status=self.status, **scale)
 
-    def silu_mul(self, x) -> torch.Tensor:
-        """bfloat16 [rows, out / 2] = silu(gate) * up, in the epilogue of the tcgen05 kernel."""
+    def silu_mul(self, x, act=ops.SILU) -> torch.Tensor:
+        """bfloat16 [rows, out / 2] = silu(gate) * up, in the epilogue of the tcgen05 kernel; with act = (alpha,
+        limit, shift) the gated activation that ops.gemm_tc describes."""
         x, scale = self._scaled(x)
         out = torch.empty((x.shape[0], self.out_features // 2), dtype=torch.bfloat16, device=x.device)
-        return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status, **scale)
+        return ops.gemm_tc(x, self.weight, out, 2 * self.gate_up_block, ops.EPI_SILU, status=self.status, act=act,
+                           **scale)
 
     def f32(self, x: torch.Tensor) -> torch.Tensor:
         """float32 [rows, out], complete sums: the tcgen05 kernel in one pass for few rows of 16-bit weights, else the

@@ -105,8 +105,9 @@ class ClampedGLU(SwiGLU):
     gated feed-forward whose gate is cut from above, whose linear branch is cut on both sides and shifted by one,
     and whose sigmoid is sharpened by alpha (1.702 gives the sigmoid form of GELU).
     params: hidden, intermediate, limit, alpha.  Tensors: <prefix>gate, up [intermediate, hidden], down
-    [hidden, intermediate].  gate and up are one matrix as in SwiGLU; the activation is a kernel of its own that
-    reads the same arrangement."""
+    [hidden, intermediate].  gate and up are one matrix as in SwiGLU, and as there the tcgen05 product applies the
+    activation in its epilogue, for few rows and for many; where that kernel does not apply, the library's product is
+    followed by the activation kernel, which reads the same arrangement."""
 
     NAMES = {"gate": "gate", "up": "up", "down": "down"}
 
@@ -114,8 +115,12 @@ class ClampedGLU(SwiGLU):
         return False
 
     def forward(self, x, ctx):
-        gu = self.gate_up.f32(x)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
-        ops.glu(gu, act, block=self.block, alpha=float(self.spec.get("alpha", 1.702)),
-                limit=float(self.spec["limit"]), shift=1.0)
+        shape = (float(self.spec.get("alpha", 1.702)), float(self.spec["limit"]), 1.0)      # alpha, limit, shift
+        if (self.gate_up.gate_up_block and self.gate_up.tc_ok and x.dtype == torch.bfloat16
+                and (self.gate_up.small(x) or fused_gate_up_pays(x.shape[0], self.gate_up.out_features))):
+            act = self.gate_up.silu_mul(x, act=shape)
+        else:
+            gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
+            act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
+            ops.glu(gu, act, block=self.block, alpha=shape[0], limit=shape[1], shift=shape[2])
         return self.down.f32(act)

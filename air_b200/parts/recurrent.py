@@ -108,7 +108,7 @@ class GatedDeltaRule(_StateMixer):
                                 ctx.q_start, ctx.slots, ctx.max_q_len)
         o = torch.empty((T, H, dv), dtype=torch.float32, device=x.device)
         ops.linear_scan(ops.SCAN_DELTA, y[:, :G * d], y[:, G * d:2 * G * d], y[:, 2 * G * d:],
-                        self._band(proj, "a"), state.state, o, ctx.q_start, ctx.slots, q_scale=d ** -0.5,
+                        self._band(proj, "a"), state.state, o, ctx.q_start, ctx.slots, ctx.token_seq, q_scale=d ** -0.5,
                         beta=self._band(proj, "b"), a_log=self.a_log, dt_bias=self.dt_bias, unit=True, unit_eps=1e-6)
         return self._finish(o, proj, ctx)
 
@@ -164,5 +164,5 @@ class GatedLinearAttention(_StateMixer):
         ops.gemm_f32(self._band(proj, "a1").contiguous(), self.a2, self.a2_bias, z)
         o = torch.empty((T, H, dv), dtype=torch.float32, device=x.device)
         ops.linear_scan(ops.SCAN_GLA, self._band(proj, "q"), self._band(proj, "k"), self._band(proj, "v"), z,
-                        state.state, o, ctx.q_start, ctx.slots, q_scale=d ** -0.5, tau=self.tau)
+                        state.state, o, ctx.q_start, ctx.slots, ctx.token_seq, q_scale=d ** -0.5, tau=self.tau)
         return self._finish(o, proj, ctx)

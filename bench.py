@@ -459,6 +459,216 @@ def kernel_prompt_elementwise(cfg, rows):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------- a second design
+# Bivizen beside the Qwen2 decoder at equal sizes (`--design bivizen`): layers that resemble a real model's, random
+# weights.  A Bivizen model here alternates its three mixers: attention, delta, attention, gla.
+def _bivizen(width, layers, heads, kv_heads, ff, vocab=32000):
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128,
+                                          "rot": {"dims": 64, "base": 1e6}, "scale": 128 ** -0.5, "softcap": 30.0,
+                                          "v_mix": True}}
+    delta = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}}
+    gla = {"type": "gla", "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    order = [att, delta, att, gla]
+    return {"architecture": "Bivizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [dict(order[i % 4], mlp=mlp) for i in range(layers)]}
+
+
+def _qwen(width, layers, heads, kv_heads, ff, vocab=32000):
+    return dict(_QWEN, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, intermediate_size=ff, rms_norm_eps=1e-5, max_window_layers=layers,
+                vocab_size=vocab)
+
+
+DESIGN_SIZES = {"2048": (2048, 8, 16, 4, 8192), "4096": (4096, 4, 32, 8, 14336)}
+
+
+def design_model(cfg, args, torch, Entry, LAST):
+    """Prefill of --prefill-tokens and decoding at --batch x --context for one configuration; the kernels' spans."""
+    from air_b200.engine.engine import Engine, EngineConfig
+    context, T, page = args.context or 2048, args.prefill_tokens, 64
+    engine = Engine.from_random(cfg, seed=0, config=EngineConfig(
+        dtype=torch.bfloat16, page_tokens=page, max_tokens=(args.batch + 1) * (context + 2 * page) + T + page,
+        max_requests=args.batch + 1))
+    randomize_cache(engine, torch)
+    vocab = engine.model.spec.vocab_size
+    prompt = torch.randint(0, vocab, (T,), generator=torch.Generator().manual_seed(7)).tolist()
+    times = []
+    for _ in range(2 + max(1, args.repeats)):
+        torch.cuda.synchronize()
+        time.sleep(args.prefill_pause_ms / 1e3)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        engine.step([Entry("p", prompt, [T - 1])])
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+        engine.finish("p")
+    pre_ms = statistics.median(times[2:])
+    requests = [f"r{i}" for i in range(args.batch)]
+    dec, clocks, launches = decode_device(engine, requests, context, args.steps, args.warmup, max(1, min(3, args.repeats)),
+                                          torch, Entry, LAST)
+    dec_ms = statistics.median(dec)
+    if args.timeline:
+        prefill_timeline(engine, prompt, torch, Entry)
+        decode_timeline(engine, requests, context, torch, Entry, LAST)
+    engine.check_status()
+    out = {"prefill_tokens": T, "prefill_ms": pre_ms, "prefill_tokens_per_s": T / (pre_ms / 1e3), "decode_batch": args.batch,
+           "context": context, "decode_ms_per_step": dec_ms, "decode_tokens_per_s": args.batch / (dec_ms / 1e3),
+           "weight_bytes": engine.model.weight_bytes(), "decode_launches": launches, "clocks": clocks}
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_kernels(width, heads, kv_heads, ff, T, batch, context):
+    """The new design's kernels alone at the layer's shapes beside the like kernel of the Qwen2 decoder, from memory
+    (512 MB written before each launch, the writes' own time subtracted): microseconds, and the share of the measured
+    copy rate (or, for the attention kernels, of the measured bf16 rate) that the algorithm's bytes (flops) make."""
+    import torch
+    from air_b200.csrc import ops
+    from air_b200.parts.attention import TiledAttention
+    from air_b200.parts.base import HostBatch
+    pk = peaks()
+    big = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph_time(calls, reps=5):
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                for c in calls:
+                    c()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / reps)
+        return statistics.median(us)
+
+    flush = lambda: big.zero_()
+    t_flush = graph_time([flush])
+    rows = []
+
+    def report(name, f, nbytes=0, flops=0):
+        us = graph_time([flush, f]) - t_flush
+        frac = (nbytes / us / 1e3 / pk["hbm_gbs"]) if nbytes else (flops / us / 1e6 / pk["bf16_tflops"])
+        rows.append({"kernel": name, "us": round(us, 1), "of": "copy rate" if nbytes else "bf16 rate", "frac": round(frac, 3)})
+        print(f"  {name:58s} {us:8.1f} us  {frac:5.2f} of the measured {'copy' if nbytes else 'bf16'} rate", flush=True)
+
+    E, H, G, d, I, P = width, heads, kv_heads, 128, ff, 64
+    dev, f32, bf = "cuda", torch.float32, torch.bfloat16
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    for label, n_rows, entries, prior in (("prompt", T, [(0, T)], 0), ("decode", batch, [(context, 1)] * batch, context)):
+        print(f"{label}: {n_rows} rows, width {E}, {H}/{G} heads of {d}, feed-forward {I}")
+        S = len(entries)
+        q_start = i32([0] + list(__import__("itertools").accumulate(n for _, n in entries)))
+        slots = i32(list(range(S)))
+        positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in entries]).to(dev)
+        seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(entries)]).to(dev)
+        blocks = -(-(prior + T) // P)
+        bt = torch.arange(S * blocks, dtype=torch.int32, device=dev).view(S, blocks).contiguous()
+        cache = torch.randn(S * blocks, 2, G, P, d, device=dev).to(bf)
+        R = n_rows
+        # the norm with the two scaled outputs of the layer before it | add + norm
+        h, a, b = (torch.randn(R, E, device=dev) for _ in range(3))
+        sa, sb, w = torch.randn(E, device=dev), torch.randn(E, device=dev), torch.ones(E, dtype=bf, device=dev)
+        x = torch.empty(R, E, dtype=bf, device=dev)
+        report("scaled_norm (stream + 2 scaled terms, norm)", lambda: ops.scaled_norm(h, [(a, sa), (b, sb)], w, 1e-5, x), R * E * 18)
+        report("  Qwen2: add_rmsnorm (stream + 1 term, norm)", lambda: ops.add_rmsnorm(h, a, w, 1e-5, x), R * E * 14)
+        # bias, rotation, value mixing, gate, cache write | bias, rotation, cache write
+        W = (H + 2 * G) * d + H
+        proj, bias = torch.randn(R, W, device=dev), torch.randn(W, device=dev)
+        freq = torch.rand(32, device=dev)
+        qo, go = torch.empty(R, H, d, dtype=bf, device=dev), torch.empty(R, H, device=dev)
+        vf, lam = torch.randn(R, G * d, device=dev), torch.tensor([0.4], device=dev)
+        flat = cache.view(cache.shape[0], -1)
+        report("qkv_prepare (bias, rotation, value mix, gates, cache write)",
+               lambda: ops.qkv_prepare(proj, bias, freq, positions, seq, bt, qo, flat, G, d, P, gate_out=go, v_first=vf,
+                                       v_mode=2, v_lambda=lam), R * (W * 4 + (H + 2 * G) * d * 2 + G * d * 4))
+        qkv, table = proj[:, :W - H].contiguous(), torch.randn(prior + T + 8, d, device=dev)
+        report("  Qwen2: qkv_rope_store", lambda: ops.qkv_rope_store(qkv, bias[:W - H].contiguous(), table, positions, seq,
+                                                                      bt, qo, cache, H, G, d), R * (W - H) * 6)
+        # attention
+        out = torch.empty_like(qo)
+        if label == "prompt":
+            planner = type("P", (TiledAttention,), {"heads": H, "window": None})()
+            plan = planner.plan(HostBatch(counts=[T], lengths=[0], slots=[0], q_start=[0, T]))
+            tiles = i32(plan.arrays["tiles"].tolist())
+            fl = 4 * H * d * (T * (T + 1) // 2)
+            report("prefill_attention_tc with a soft cap", lambda: ops.prefill_attention_tc(qo, cache, bt, tiles, out, None, d ** -0.5, softcap=30.0), flops=fl)
+            report("  Qwen2: prefill_attention_tc", lambda: ops.prefill_attention_tc(qo, cache, bt, tiles, out, None, d ** -0.5), flops=fl)
+        else:
+            nb = batch * context * 2 * G * d * 2
+            report("decode_attention with a soft cap", lambda: ops.decode_attention(qo, cache, bt, seq, positions, out, None, d ** -0.5, softcap=30.0), nb)
+            report("  Qwen2: decode_attention", lambda: ops.decode_attention(qo, cache, bt, seq, positions, out, None, d ** -0.5), nb)
+        report("head_gate", lambda: ops.head_gate(out, go, seq), R * H * d * 4)
+        # the state mixers: convolution, scans, gated norm (no like kernel in the Qwen2 decoder)
+        Gd, Hs = H // 2, H
+        C = 2 * Gd * d + Hs * d
+        xs, cw = torch.randn(R, C + 2 * Hs, device=dev), torch.randn(C, 4, device=dev)
+        tail, y = torch.zeros(S, C, 3, device=dev), torch.empty(R, C, device=dev)
+        longest = max(n for _, n in entries)
+        report("short_conv_silu (4 taps)", lambda: ops.short_conv_silu(xs[:, :C], cw, tail, y, q_start, slots, longest),
+               R * C * 8 + (S * C * 24 if label == "decode" else 0))
+        state, o = torch.zeros(S, Hs, d, d, device=dev), torch.empty(R, Hs, d, device=dev)
+        al, dtb = torch.zeros(Hs, device=dev), torch.zeros(Hs, device=dev)
+        scan_bytes = R * (C + Hs * d) * 4 + S * Hs * d * d * 8
+        report("linear_scan, delta rule", lambda: ops.linear_scan(
+            ops.SCAN_DELTA, y[:, :Gd * d], y[:, Gd * d:2 * Gd * d], y[:, 2 * Gd * d:], xs[:, C:C + Hs], state, o, q_start,
+            slots, seq, q_scale=d ** -0.5, beta=xs[:, C + Hs:], a_log=al, dt_bias=dtb, unit=True), scan_bytes)
+        Hg, dvg = H // 2, 256
+        qg, vg, zg = torch.randn(R, 2 * Hg * d, device=dev), torch.randn(R, Hg * dvg, device=dev), torch.randn(R, Hg * d, device=dev)
+        sg, og = torch.zeros(S, Hg, d, dvg, device=dev), torch.empty(R, Hg, dvg, device=dev)
+        report("linear_scan, gated linear attention", lambda: ops.linear_scan(
+            ops.SCAN_GLA, qg[:, :Hg * d], qg[:, Hg * d:], vg, zg, sg, og, q_start, slots, seq, q_scale=d ** -0.5, tau=16.0),
+            R * (3 * Hg * d + 2 * Hg * dvg) * 4 + S * Hg * d * dvg * 8)
+        gate, nw = torch.randn(R, Hs * d, device=dev), torch.ones(d, device=dev)
+        yo = torch.empty(R, Hs * d, dtype=bf, device=dev)
+        report("gated_rmsnorm", lambda: ops.gated_rmsnorm(o, gate, nw, 1e-5, yo, seq), R * Hs * d * 10)
+        # the feed-forward's activation
+        gu32, act = torch.randn(R, 2 * I, device=dev), torch.empty(R, I, dtype=bf, device=dev)
+        report("glu with limits (float32 product in)", lambda: ops.glu(gu32, act, block=128, alpha=1.702, limit=7.0, shift=1.0), R * I * 10)
+        gu16 = gu32.to(bf)
+        report("  Qwen2: silu_mul (bfloat16 product in)", lambda: ops.silu_mul(gu16, act, block=128), R * I * 6)
+        del cache
+    return rows
+
+
+def design_bench(args):
+    import torch
+    from air_b200.engine.batch import Entry, LAST_SAMPLED
+    if args.design != "bivizen":
+        print(json.dumps({"error": f"--design {args.design}: bivizen is the design that is compared"}))
+        return 2
+    record = {"design": "Bivizen", "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    context = args.context or 2048
+    for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+        width, layers, heads, kv_heads, ff = DESIGN_SIZES[name]
+        if args.layers:
+            layers = args.layers
+        size = {"width": width, "layers": layers, "heads": heads, "kv_heads": kv_heads, "ff": ff}
+        for label, cfg in (("bivizen", _bivizen(width, layers, heads, kv_heads, ff)), ("qwen2", _qwen(width, layers, heads, kv_heads, ff))):
+            print(f"--- {label} at width {width}, {layers} layers", flush=True)
+            size[label] = design_model(cfg, args, torch, Entry, LAST_SAMPLED)
+        if not args.skip_kernels:
+            size["kernels"] = design_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
+        record["sizes"][name] = size
+    text = json.dumps(record)
+    print(text)
+    if args.output:
+        with open(args.output, "w") as f:
+            f.write(text + "\n")
+    return 0
+
+
 def reference_arm(args, cfg, context):
     """EmersonDowell/AIR's CUDA executor on the same shape: its own prefill and step_greedy_batch."""
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -529,6 +739,11 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
     ap.add_argument("--kernel", default="", help="prefill_attention, or prompt_elementwise (at --prefill-tokens rows): time those kernels alone and exit")
+    ap.add_argument("--design", default="", help="bivizen: prefill and decode of that design beside the Qwen2 decoder at "
+                    "equal sizes, and its kernels alone beside the like kernels (another line of output; the default "
+                    "workload is not run)")
+    ap.add_argument("--design-sizes", default="", help="with --design: which of the sizes 2048,4096 (default: both)")
+    ap.add_argument("--skip-kernels", action="store_true", help="with --design: the models only")
     ap.add_argument("--timeline", action="store_true", help="also print the kernels' spans inside the decode graph and in the prefill step")
     args = ap.parse_args()
     if args.gpus != 1:
@@ -536,6 +751,8 @@ def main():
                           "n_gpus": args.gpus}))
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        return design_bench(args)
     if args.shape in SHAPES:
         cfg, context = dict(SHAPES[args.shape]), args.context or CONTEXTS[args.shape]
     else:

@@ -88,7 +88,8 @@ def test_delta_rule_scan(H, G, d, dv):
             rows = [np.concatenate([seqs[r][i][at:at + n] for r in (1, 0)]) for i in range(5)]
             out = torch.empty((2 * n, H, dv), device=DEV)
             ops.linear_scan(ops.SCAN_DELTA, dev(rows[0]), dev(rows[1]), dev(rows[2]), dev(rows[3]), state, out,
-                            i32([0, n, 2 * n]), i32([1, 0]), q_scale=d ** -0.5, beta=dev(rows[4]), a_log=dev(a_log),
+                            i32([0, n, 2 * n]), i32([1, 0]), i32([1] * n + [0] * n), q_scale=d ** -0.5, beta=dev(rows[4]),
+                            a_log=dev(a_log),
                             dt_bias=dev(dt_bias), unit=True)
             out = out.cpu().numpy()
             for j, r in enumerate((1, 0)):
@@ -113,7 +114,7 @@ def test_gated_linear_attention_scan(H, d, dv, tau):
         for n in cuts:
             out = torch.empty((n, H, dv), device=DEV)
             ops.linear_scan(ops.SCAN_GLA, dev(q[at:at + n]), dev(k[at:at + n]), dev(v[at:at + n]), dev(z[at:at + n]),
-                            state, out, i32([0, n]), i32([3]), q_scale=d ** -0.5, tau=tau)
+                            state, out, i32([0, n]), i32([3]), i32([3] * n), q_scale=d ** -0.5, tau=tau)
             assert np.abs(out.cpu().numpy() - want[at:at + n]).max() < 3e-5 * max(1.0, np.abs(want).max())
             at += n
         assert float(state[0].min()) == 3.0              # other requests' states are not touched
