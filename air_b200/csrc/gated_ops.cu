@@ -5,7 +5,8 @@
 //                       shift = 0, limit = 0 is SiLU(gate) * up.  The input [T, 2I] holds blocks of `block` gate
 //                       columns and `block` up columns in turn.
 //   head_gate_kernel    x[t, h, :] *= gate[t, h], for attention kernels that do not multiply by a gate as they write
-//   scaled_norm_kernel  x = h + sa * a + sb * b (float32; a scale per column, each term optional), written back into
+//   scaled_norm_kernel  x = h + sa * a + sb * b (float32; a scale per column, each term optional; a term may come as
+//                       the partial sums of a split product, [parts, T, E], which are added in order), written back into
 //                       the stream h when no rows are named, and out = x / sqrt(mean(x^2) + eps) * w.  With `rows`
 //                       the kernel reads h[rows[r]] and leaves h alone.  Without w it only completes the stream.
 #include "common.cuh"
@@ -43,9 +44,9 @@ __global__ void head_gate_kernel(TX* __restrict__ x, const float* __restrict__ g
 
 template <typename TW, typename TO>
 __global__ void scaled_norm_kernel(float* __restrict__ h, const float* __restrict__ a, const float* __restrict__ sa,
-                                   const float* __restrict__ b, const float* __restrict__ sb,
-                                   const TW* __restrict__ w, TO* __restrict__ out, const int* __restrict__ rows,
-                                   int E, float eps) {
+                                   int a_parts, const float* __restrict__ b, const float* __restrict__ sb, int b_parts,
+                                   size_t part_stride, const TW* __restrict__ w, TO* __restrict__ out,
+                                   const int* __restrict__ rows, int E, float eps) {
     __shared__ float scratch[32];
     extern __shared__ float xrow[];
     pdl_enter(TR_SCALED_NORM);
@@ -54,8 +55,16 @@ __global__ void scaled_norm_kernel(float* __restrict__ h, const float* __restric
     float ss = 0.f;
     for (int i = threadIdx.x; i < E; i += blockDim.x) {
         float x = h[src + i];
-        if (a) x += (sa ? sa[i] : 1.f) * a[src + i];
-        if (b) x += (sb ? sb[i] : 1.f) * b[src + i];
+        if (a) {
+            float t = a[src + i];
+            for (int p = 1; p < a_parts; ++p) t += a[p * part_stride + src + i];
+            x += (sa ? sa[i] : 1.f) * t;
+        }
+        if (b) {
+            float t = b[src + i];
+            for (int p = 1; p < b_parts; ++p) t += b[p * part_stride + src + i];
+            x += (sb ? sb[i] : 1.f) * t;
+        }
         xrow[i] = x;
         ss += x * x;
         if (!rows && (a || b)) h[src + i] = x;
@@ -92,9 +101,9 @@ AIR_API int air_head_gate(void* x, int dtype, const float* gate, const int* toke
     return 0;
 }
 
-AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, const float* b, const float* sb, const void* w,
-                            int w_dtype, void* out, int out_dtype, const int* rows, int R, int E, float eps,
-                            cudaStream_t stream) {
+AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, int a_parts, const float* b, const float* sb,
+                            int b_parts, long long part_stride, const void* w, int w_dtype, void* out, int out_dtype,
+                            const int* rows, int R, int E, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
     // few rows: a block as wide as half a row, so that a row's loads are all under way at once
     int threads = E >= 1024 ? 256 : 128;
@@ -104,7 +113,8 @@ AIR_API int air_scaled_norm(float* h, const float* a, const float* sa, const flo
     AIR_DISPATCH(w_dtype, TW, AIR_DISPATCH(out_dtype, TO, {
         auto kernel = air::scaled_norm_kernel<TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return air::launch(kernel, R, threads, smem, stream, h, a, sa, b, sb, (const TW*)w, (TO*)out, rows, E, eps);
+        return air::launch(kernel, R, threads, smem, stream, h, a, sa, a_parts, b, sb, b_parts, (size_t)part_stride,
+                           (const TW*)w, (TO*)out, rows, E, eps);
     }));
     return 0;
 }

@@ -40,8 +40,8 @@ _SIGNATURES = {
     "air_gated_rmsnorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float,
                           c_void_p],
     "air_glu": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p],
-    "air_scaled_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
-                        c_int, c_int, c_float, c_void_p],
+    "air_scaled_norm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int,
+                        c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p],
     "air_table_update": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "air_decode_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -516,8 +516,8 @@ def glu(gate_up, out, block=None, alpha=1.0, limit=0.0, shift=0.0):
 
 
 def scaled_norm(h, terms, weight, eps, out, rows=None):
-    """x = h + sum of scale * term over up to two terms (term float32 [T, E], scale float32 [E] or None), written
-    into h when rows is None; out = x / sqrt(mean(x^2) + eps) * weight.  With rows: out[r] is that of row rows[r],
+    """x = h + sum of scale * term over up to two terms (term float32 [T, E], or [parts, T, E] partial sums that are
+    added in order; scale float32 [E] or None), written into h when rows is None; out = x / sqrt(mean(x^2) + eps) * weight.  With rows: out[r] is that of row rows[r],
     h unchanged.  weight None (and out None): only the stream is completed."""
     E = h.shape[-1]
     _req(h, "h", (torch.float32,), (None, E))
@@ -526,18 +526,21 @@ def scaled_norm(h, terms, weight, eps, out, rows=None):
         raise KernelError("scaled_norm: at most two terms")
     ptrs = []
     for term, scale in terms + [(None, None)] * (2 - len(terms)):
+        parts = 1
         if term is not None:
-            _req(term, "term", (torch.float32,), tuple(h.shape))
+            parts = 1 if term.dim() == 2 else term.shape[0]
+            _req(term, "term", (torch.float32,), tuple(h.shape) if term.dim() == 2 else (parts,) + tuple(h.shape))
         if scale is not None:
             _req(scale, "scale", (torch.float32,), (E,))
-        ptrs += [_ptr(term), _ptr(scale)]
+        ptrs += [_ptr(term), _ptr(scale), parts]
     R = h.shape[0] if rows is None else rows.shape[0]
     if rows is not None:
         _req(rows, "rows", _I32)
     if weight is not None:
         _req(weight, "weight", _FLOATS, (E,))
         _req(out, "out", _FLOATS, (R, E))
-    _check(_get("air_scaled_norm")(h.data_ptr(), *ptrs, _ptr(weight), _DT[weight.dtype] if weight is not None else 0,
+    _check(_get("air_scaled_norm")(h.data_ptr(), *ptrs, h.numel(), _ptr(weight),
+                                   _DT[weight.dtype] if weight is not None else 0,
                                    _ptr(out) if weight is not None else None,
                                    _DT[out.dtype] if weight is not None else 0, _ptr(rows), R, E, float(eps),
                                    _stream()), "scaled_norm")

@@ -192,7 +192,8 @@ class PreNormed:
 @dataclass
 class ScaledSum:
     """What parts that stand side by side add to the stream together: the sum of scale * term over `terms`, a list
-    of (float32 [T, hidden], float32 [hidden] or None: a scale per column).  A form of a norm's `delta`: the norm
+    of (float32 [T, hidden], or [parts, T, hidden] partial sums of a split product; float32 [hidden] or None: a scale
+    per column).  A form of a norm's `delta`: the norm
     that follows completes the stream with it (Norm.add_delta, or a kernel of its own that also normalises)."""
     terms: list
 

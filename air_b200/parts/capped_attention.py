@@ -128,4 +128,4 @@ class CappedAttention(TiledAttention, Mixer):
         else:
             ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale,
                                     softcap=self.softcap, gate=gate, kv_heads=G, page_tokens=P)
-        return self.o.f32(out.view(T, H * dv))
+        return self.o.f32_sums(out.view(T, H * dv))

@@ -107,6 +107,11 @@ class Linear:
         product that __call__ picks."""
         return self.full(x) if self.small(x) else self(x, torch.float32)
 
+    def f32_sums(self, x: torch.Tensor) -> torch.Tensor:
+        """float32 [rows, out], or for few rows of 16-bit weights [parts, rows, out]: the partial sums of the product
+        with its k range split over all SMs, for a consumer that adds them."""
+        return self.partial(x) if self.small(x) else self(x, torch.float32)
+
     def adds_into(self, x: torch.Tensor, residual) -> bool:
         """Whether add_into() applies: 16-bit weights, a float32 stream of this product's shape."""
         return (residual is not None and self.weight.dtype != torch.float32 and x.dtype == self.weight.dtype

@@ -123,4 +123,4 @@ class ClampedGLU(SwiGLU):
             gu = self.gate_up(x, torch.float32 if self.rt.is_fp32 else self.rt.dtype)
             act = torch.empty((x.shape[0], self.intermediate), dtype=self.rt.dtype, device=x.device)
             ops.glu(gu, act, block=self.block, alpha=shape[0], limit=shape[1], shift=shape[2])
-        return self.down.f32(act)
+        return self.down.f32_sums(act)

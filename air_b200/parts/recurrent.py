@@ -37,7 +37,7 @@ class _StateMixer(Mixer):
         T = o.shape[0]
         y = torch.empty((T, self.heads * self.v_dim), dtype=self.rt.dtype, device=o.device)
         ops.gated_rmsnorm(o, self._band(proj, "g"), self.norm_weight, self.eps, y, ctx.token_seq)
-        return self.o.f32(y)
+        return self.o.f32_sums(y)
 
 
 @register_mixer("gated_delta")

@@ -61,6 +61,21 @@ def test_rank_of_the_decay_projection_comes_from_the_file(tmp_path):
     assert load_config(str(other)).layers[0].rank == 4
 
 
+def test_command_line_inspects_and_writes_a_bivizen_folder(tmp_path, capsys):
+    from air_b200 import cli
+    assert cli.main(["inspect", bu.model_folder("Q")]) == 0
+    shown = json.loads(capsys.readouterr().out)
+    assert shown["architecture"] == "Bivizen" and shown["config"]["layers"][1]["mixer"]["conv"] == 2
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(bu.CONFIGS["S"]))
+    assert cli.main(["random", str(cfg), str(tmp_path / "model"), "--seed", "3"]) == 0
+    capsys.readouterr()
+    assert cli.main(["inspect", str(tmp_path / "model"), "--tensors"]) == 0
+    assert "l0.mix.vmix\t[]" in capsys.readouterr().out
+    config, tensors = plain.read_model(str(tmp_path / "model"))          # the oracle reads what the engine wrote
+    assert np.isfinite(plain.forward(config, tensors, [1, 2, 3])).all()
+
+
 # ----------------------------------------------------------------------------- the oracle's mechanisms
 def test_plain_short_conv_is_a_causal_correlation():
     rng = np.random.default_rng(0)

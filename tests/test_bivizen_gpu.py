@@ -362,3 +362,11 @@ def test_trace_runner_program_and_command_line():
         util.run_trace_program(bu.model_folder(name), "float32", steps, util.peak_tokens(steps), out)
         got = util.collect(steps, out, bu.CONFIGS[name]["vocab"])
     bu.check(got, name, streams, "float32")
+
+
+def test_command_line_generates(capsys):
+    from air_b200 import cli
+    prompt = bu.tokens_for("Q", 9, 70)
+    assert cli.main(["cuda", bu.model_folder("Q"), ",".join(map(str, prompt)), "--tokens", "6", "--dtype", "float32",
+                     "--no-stop-on-eos"]) == 0
+    assert capsys.readouterr().out.strip() == ",".join(map(str, bu.plain_greedy("Q", prompt, 6)))
