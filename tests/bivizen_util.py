@@ -63,6 +63,53 @@ CONFIGS = {
 SEEDS = {"P": 11, "Q": 12, "R": 13, "S": 14}
 
 
+def random_config(seed, tensor_core_heads=False):
+    """A configuration drawn at random: 2 to 7 layers of any order, every size, option and constant from a list that
+    includes 1, equal and unequal sizes and sizes that are no powers of two.  tensor_core_heads: attention heads of
+    64 or 128 with values of the same size (the heads that the tensor-core attention kernels take in bfloat16)."""
+    rng = np.random.default_rng(seed)
+    width = int(rng.choice([48, 64, 72, 96, 128, 160, 192, 256, 320]))
+    layers, shape = [], None
+    for _ in range(int(rng.integers(2, 8))):
+        kind = rng.choice(["attention", "delta", "gla"], p=[0.45, 0.3, 0.25])
+        if kind == "attention":
+            if shape is None or rng.random() < 0.3:
+                kv, rep = int(rng.choice([1, 2, 3, 4])), int(rng.choice([1, 2, 4]))
+                dim = int(rng.choice([8, 16, 24, 32, 40, 48, 64, 96, 128]))
+                vdim = int(rng.choice([8, 16, 24, 32, 48, 64, 128, dim, dim]))
+                if tensor_core_heads:
+                    dim = vdim = int(rng.choice([64, 128]))
+                shape = (kv * rep, kv, dim, vdim)
+            H, G, dim, vdim = shape
+            rot = None
+            if rng.random() < 0.85:
+                rot = (int(rng.choice([d for d in (2, 4, 8, 16, 24, 32, 64, dim) if d <= dim and d % 2 == 0])),
+                       float(rng.choice([100.0, 10000.0, 250000.0, 1e6])))
+            layer = attention(H, G, dim, vdim, float(rng.choice([dim ** -0.5, 0.1, 0.25])),
+                              softcap=float(rng.choice([0.0, 3.0, 8.0, 20.0, 50.0])), rot=rot, v_mix=bool(rng.random() < 0.6))
+        elif kind == "delta":
+            kv, rep = int(rng.choice([1, 2, 3])), int(rng.choice([1, 2, 4]))
+            layer = delta(kv * rep, kv, int(rng.choice([8, 16, 24, 32, 48, 64, 128])),
+                          int(rng.choice([8, 16, 20, 32, 64, 96, 128])), int(rng.integers(1, 7)))
+        else:
+            layer = gla(int(rng.choice([1, 2, 3, 4])), int(rng.choice([8, 16, 24, 32, 64])),
+                        int(rng.choice([8, 16, 40, 64, 128])), float(rng.choice([1.0, 4.0, 16.0, 32.0])),
+                        int(rng.choice([2, 4, 8, 16, 24])))
+        if rng.random() < 0.15:
+            layers.append(with_mlp(layer, None, None))
+        else:
+            layers.append(with_mlp(layer, int(rng.choice([64, 96, 100, 128, 160, 200, 256, 384, 512])),
+                                   float(rng.choice([0.7, 1.0, 2.0, 5.0]))))
+    first = None                 # layers that mix values must agree in the values' shape
+    for l in layers:
+        if l["type"] == "attention" and l["mixer"].get("v_mix"):
+            key = (l["mixer"]["kv_heads"], l["mixer"]["vdim"])
+            first = first or key
+            if key != first:
+                l["mixer"]["v_mix"] = False
+    return config(int(rng.integers(50, 700)), width, float(rng.choice([1e-6, 1e-5, 1e-4])), layers)
+
+
 def bf16(a):
     """Rounded to values that bfloat16 holds (ties to even), as float32."""
     u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
@@ -139,6 +186,9 @@ def model_folder(name):
     from air_b200.weights.loader import write_model_folder
     d = tempfile.TemporaryDirectory(prefix=f"air_b200_bivizen_{name}_")
     _tmp.append(d)
+    if name not in CONFIGS:      # "random<seed>" / "tensorcore<seed>": drawn at random
+        seed = int(name.lstrip("randomtensorcore"))
+        CONFIGS[name], SEEDS[name] = random_config(seed, tensor_core_heads=name.startswith("tensorcore")), seed
     cfg = CONFIGS[name]
     tensors = {n: torch.from_numpy(np.ascontiguousarray(a)).reshape(a.shape).to(torch.bfloat16)
                for n, a in draw_tensors(cfg, SEEDS[name]).items()}

@@ -275,6 +275,28 @@ def test_unequal_requests_together_with_pages_and_slots_used_again(name, dtype, 
         assert group.pool.takes > group.pool.num_pages, "pages were used again"
 
 
+@pytest.mark.parametrize("name", ["random1", "random4", "random9", "random13", "tensorcore5", "tensorcore11"])
+def test_configurations_drawn_at_random(name):
+    """Layer orders, sizes and constants that nobody chose (bivizen_util.random_config): whole prompts and a mixed
+    schedule through three slots, float32 within its tolerance; bfloat16 must agree with itself across schedules (its
+    distance from the oracle depends on how a drawn model amplifies rounding)."""
+    folder = bu.model_folder(name)
+    streams = {f"{name}_{i}": bu.tokens_for(name, n, 80 + i) for i, n in enumerate((150, 3, 70, 1, 97))}
+    whole = util.trace_whole(streams)
+    mixed = util.trace_mixed(streams, seed=5, live=3, tail=20)
+    got, _ = replay(name, "float32", whole, page_tokens=64)
+    bu.check(got, name, streams, "float32")
+    got, _ = replay(name, "float32", mixed, page_tokens=64, max_requests=3)
+    bu.check(got, name, streams, "float32")
+    a, _ = replay(name, "bfloat16", whole, page_tokens=64)
+    b, _ = replay(name, "bfloat16", mixed, page_tokens=64, max_requests=3)
+    for key, row in a.items():
+        ref = bu.plain_logits(name, streams[key[0]])[key[1]]
+        scale = max(1.0, float(np.abs(bu.plain_logits(name, streams[key[0]])).max()))
+        assert np.isfinite(b[key]).all()
+        assert np.abs(b[key] - row).max() <= max(2 * np.abs(row - ref).max(), 1e-2 * scale), key
+
+
 @pytest.mark.parametrize("name", ["P", "R"])
 def test_float32_does_not_depend_on_the_cut_or_the_batch(name):
     streams = streams_for(name, 30, (97, 40, 131))
