@@ -57,11 +57,13 @@ __global__ void scaled_norm_kernel(float* __restrict__ h, const float* __restric
         float x = h[src + i];
         if (a) {
             float t = a[src + i];
-            for (int p = 1; p < a_parts; ++p) t += a[p * part_stride + src + i];
+#pragma unroll 4
+            for (int p = 1; p < a_parts; ++p) t += a[p * part_stride + src + i];      // (loads ahead, sums in order)
             x += (sa ? sa[i] : 1.f) * t;
         }
         if (b) {
             float t = b[src + i];
+#pragma unroll 4
             for (int p = 1; p < b_parts; ++p) t += b[p * part_stride + src + i];
             x += (sb ? sb[i] : 1.f) * t;
         }

@@ -569,7 +569,10 @@ def design_kernels(width, heads, kv_heads, ff, T, batch, context):
     for label, n_rows, entries, prior in (("prompt", T, [(0, T)], 0), ("decode", batch, [(context, 1)] * batch, context)):
         print(f"{label}: {n_rows} rows, width {E}, {H}/{G} heads of {d}, feed-forward {I}")
         S = len(entries)
-        q_start = i32([0] + list(__import__("itertools").accumulate(n for _, n in entries)))
+        starts = [0]
+        for _, n in entries:
+            starts.append(starts[-1] + n)
+        q_start = i32(starts)
         slots = i32(list(range(S)))
         positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in entries]).to(dev)
         seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(entries)]).to(dev)

@@ -5,8 +5,6 @@ import tempfile
 
 import numpy as np
 
-ATT = dict(type="attention")
-
 
 def attention(heads, kv_heads, dim, vdim, scale, softcap=0.0, rot=None, v_mix=False):
     m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, v_mix=v_mix)
