@@ -76,11 +76,11 @@ def bivizen_spec(config: BivizenConfig) -> ModelSpec:
             mixer = PartSpec("gla", {"hidden": e, "heads": l.heads, "head_dim": l.dim, "v_dim": l.vdim, "tau": l.tau,
                                      "rank": l.rank, "eps": config.eps})
         parts = {"norm": norm, "mixer": mixer}
-        names = {"norm": "norm1", "mixer": "mix.", "mixer_scale": "ls1"}
+        names = {"norm": "norm1", "mixer": "mix.", "mixer_scale": "ls1", "feed_forward_scale": "ls2"}
         if l.mlp is not None:
             parts["feed_forward"] = PartSpec("clamped_glu", {"hidden": e, "intermediate": l.mlp.ff,
                                                              "limit": l.mlp.limit, "alpha": 1.702})
-            names.update(feed_forward="mlp.", feed_forward_scale="ls2")
+            names.update(feed_forward="mlp.")
         layers.append(BlockSpec(kind="parallel", prefix=f"l{i}.", parts=parts, names=names))
     return ModelSpec(
         architecture=config.architecture, hidden_size=e, vocab_size=config.vocab, max_positions=config.max_positions,

@@ -102,6 +102,9 @@ class ParallelBlock(Block):
                                                                                   spec.name("feed_forward"))
         self.scale_names = {role: spec.prefix + spec.names[role + "_scale"] for role in ("mixer", "feed_forward")
                             if role + "_scale" in spec.names and (role == "mixer" or self.feed_forward is not None)}
+        # a scale that is named for a feed-forward that the layer does not have: taken if the file has it, not used
+        self.idle_names = [spec.prefix + spec.names["feed_forward_scale"]] \
+            if "feed_forward_scale" in spec.names and self.feed_forward is None else []
         self.scales = {}
 
     def parts(self):
@@ -111,7 +114,8 @@ class ParallelBlock(Block):
         from ..weights.loader import TensorSpec
         size = self.spec.part("norm")["size"]
         return super().tensor_specs() + [TensorSpec(name, (size,), init="one_plus_normal", wide=True)
-                                         for name in self.scale_names.values()]
+                                         for name in self.scale_names.values()] + \
+            [TensorSpec(name, (size,), init="one_plus_normal", wide=True, optional=True) for name in self.idle_names]
 
     def load(self, tensors, rt):
         super().load(tensors, rt)
