@@ -405,8 +405,8 @@ def short_conv_silu(x, weight, state, y, q_start, slots, max_tokens):
     _req(slots, "slots", _I32)
     if x.shape[1] != C:
         raise KernelError(f"short_conv_silu: x has {x.shape[1]} channels, the weight {C}")
-    if not (1 <= taps <= 8):
-        raise KernelError(f"short_conv_silu: {taps} taps (the kernel takes 1 to 8)")
+    if not (1 <= taps <= 16):
+        raise KernelError(f"short_conv_silu: {taps} taps (the kernel takes 1 to 16)")
     _check(_get("air_short_conv_silu")(xp, ld, weight.data_ptr(), state.data_ptr(), y.data_ptr(), q_start.data_ptr(),
                                        slots.data_ptr(), slots.shape[0], C, taps, int(max_tokens), _stream()),
            "short_conv_silu")

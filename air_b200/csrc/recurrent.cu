@@ -18,7 +18,7 @@
 
 namespace air {
 
-constexpr int CONV_MAX_TAPS = 8;
+constexpr int CONV_MAX_TAPS = 16;
 constexpr int CONV_THREADS = 128;
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
@@ -42,44 +42,41 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, const float* __restr
     if (t0 >= n && blockIdx.z > 0) return;
     const int t1 = min(n, t0 + chunk);
     const int keep = taps - 1;
-    float wv[CONV_MAX_TAPS], win[CONV_MAX_TAPS], old[CONV_MAX_TAPS];
-#pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
-        wv[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
-        win[j] = 0.f;
-        old[j] = 0.f;
-    }
+    // Weights and window are held right-aligned in arrays of the largest size, so that every index is a
+    // compile-time number (registers): wv[M - 1] is the current token's weight, win[j] the input M - 1 - j tokens
+    // before the next one; the places in front of the taps hold zeros.
+    constexpr int M = CONV_MAX_TAPS;
+    const int lead = M - 1 - keep;            // unused places in front
+    float wv[M], win[M - 1];
     float* st = state + ((size_t)slot * C + c) * keep;
-    // win[i]: the input (taps - 1 - i) tokens before the next one
 #pragma unroll
-    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
-        if (i < keep) {
-            const int idx = t0 - keep + i;
-            win[i] = idx >= 0 ? x[(size_t)(q0 + idx) * ld + c] : st[keep + idx];
-            old[i] = win[i];
+    for (int j = 0; j < M; ++j) wv[j] = j >= lead ? w[(size_t)c * taps + (j - lead)] : 0.f;
+#pragma unroll
+    for (int j = 0; j < M - 1; ++j) {
+        win[j] = 0.f;
+        if (j >= lead) {
+            const int idx = t0 - keep + (j - lead);      // the portion's token at this place, or (negative) the state's
+            win[j] = idx >= 0 ? x[(size_t)(q0 + idx) * ld + c] : st[keep + idx];
         }
     }
     for (int t = t0; t < t1; ++t) {
         const float cur = x[(size_t)(q0 + t) * ld + c];
-        float acc = 0.f;
+        float acc = wv[M - 1] * cur;
 #pragma unroll
-        for (int i = 0; i < CONV_MAX_TAPS - 1; ++i)
-            if (i < keep) acc = fmaf(wv[i], win[i], acc);
-        acc = fmaf(wv[keep], cur, acc);
+        for (int j = 0; j < M - 1; ++j)
+            if (j >= lead) acc = fmaf(wv[j], win[j], acc);
         y[(size_t)(q0 + t) * C + c] = silu_f(acc);
 #pragma unroll
-        for (int i = 0; i < CONV_MAX_TAPS - 2; ++i)
-            if (i + 1 < keep) win[i] = win[i + 1];
-        if (keep > 0) win[keep - 1] = cur;
+        for (int j = 0; j < M - 2; ++j) win[j] = win[j + 1];
+        win[M - 2] = cur;
     }
     if (blockIdx.z == 0) {
-        // the state after the portion: its last taps - 1 inputs, or older ones from the state as it was
+        // The state after the portion: its last taps - 1 inputs.  A portion that this thread has taken whole leaves
+        // them in the window (older ones from the state as it was included); a longer one has them all among its tokens
+        // (a chunk is longer than the window).
 #pragma unroll
-        for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
-            if (i < keep) {
-                const int idx = n - keep + i;
-                st[i] = idx >= 0 ? x[(size_t)(q0 + idx) * ld + c] : old[i + n];
-            }
+        for (int j = 0; j < M - 1; ++j) {
+            if (j >= lead) st[j - lead] = n <= chunk ? win[j] : x[(size_t)(q0 + n - keep + (j - lead)) * ld + c];
         }
     }
 }

@@ -64,8 +64,8 @@ class GatedDeltaRule(_StateMixer):
         self.head_dim, self.v_dim, self.taps, self.eps = p["head_dim"], p["v_dim"], int(p["conv"]), float(p["eps"])
         if self.heads % self.kv_heads:
             raise ConfigError("data_error", "gated_delta: heads must be a multiple of kv_heads")
-        if not (1 <= self.taps <= 8):
-            raise ConfigError("unsupported", f"gated_delta: a convolution of {self.taps} taps (the kernel takes 1 to 8)")
+        if not (1 <= self.taps <= 16):
+            raise ConfigError("unsupported", f"gated_delta: a convolution of {self.taps} taps (the kernel takes 1 to 16)")
         if self.head_dim > 1024:
             raise ConfigError("unsupported", f"gated_delta: {self.head_dim} key channels per head (up to 1,024)")
         self.channels = 2 * self.kv_heads * self.head_dim + self.heads * self.v_dim

@@ -25,7 +25,7 @@ def i32(a):
 
 
 # ----------------------------------------------------------------------------- mechanisms alone
-@pytest.mark.parametrize("taps,channels", [(4, 70), (2, 33), (1, 16), (7, 130)])
+@pytest.mark.parametrize("taps,channels", [(4, 70), (2, 33), (1, 16), (7, 130), (13, 40)])
 def test_short_convolution_with_state_over_portions(taps, channels):
     """Three requests of unequal length in one batch per step, portions of 1 to 40 tokens (shorter than the taps
     too), one slot used twice: the second request in it must not see the first one's inputs."""
