@@ -98,6 +98,7 @@ class Group:
     key: Hashable                 # the needs' group key
     window: Optional[int]         # None: every page is kept until the request ends
     pool: PagePool
+    need: Optional[CacheNeed] = None      # the need that opened the group: says which keys later queries can see
     runs: List[int] = field(default_factory=list)
 
 
@@ -165,7 +166,7 @@ class CacheManager:
         for i, g in enumerate(self.groups):
             if g.key == key:
                 return i
-        self.groups.append(Group(key, need.window, PagePool(self.num_pages)))
+        self.groups.append(Group(key, need.window, PagePool(self.num_pages), need=need))
         return len(self.groups) - 1
 
     @staticmethod
@@ -204,8 +205,10 @@ class CacheManager:
     def pages_needed(self, tokens: int) -> int:
         return -(-tokens // self.page_tokens)
 
-    def _first_live_block(self, window: Optional[int], length: int) -> int:
+    def _first_live_block(self, window: Optional[int], length: int, need: Optional[CacheNeed] = None) -> int:
         """Blocks below this hold only tokens that no query at position >= length can see."""
+        if need is not None:
+            return need.first_live(length) // self.page_tokens
         if window is None:
             return 0
         return max(0, length - window + 1) // self.page_tokens
@@ -242,7 +245,7 @@ class CacheManager:
         if self.groups and seq.length > len(seq.pages[0]) * self.page_tokens:
             raise CacheError(f"request {request!r} holds fewer pages than its length needs")
         for gi, g in enumerate(self.groups):
-            first = self._first_live_block(g.window, seq.length)
+            first = self._first_live_block(g.window, seq.length, g.need)
             pages = seq.pages[gi]
             for b in range(min(first, len(pages))):
                 if pages[b] >= 0:

@@ -1,5 +1,6 @@
 from .model_config import ConfigError, Qwen2Config
 from .bivizen_config import BivizenConfig
+from .tomodra_config import TomodraConfig
 from . import architectures  # registers the known architectures
 import json
 import os

@@ -7,6 +7,7 @@ from ..parts.registry import register_architecture
 from ..parts.spec import BlockSpec, ModelSpec, PartSpec, RunStep
 from .bivizen_config import BivizenConfig
 from .model_config import Qwen2Config
+from .tomodra_config import TomodraConfig
 
 
 # what follows "model.layers.N." in the names of each part's tensors
@@ -89,3 +90,55 @@ def bivizen_spec(config: BivizenConfig) -> ModelSpec:
 
 
 register_architecture("Bivizen", BivizenConfig, bivizen_spec)
+
+
+def tomodra_spec(config: TomodraConfig) -> ModelSpec:
+    """Tomodra: every layer normalises after the sum (x = rms(alpha x + mixer(x)) w1; x = rms(alpha x + ff(x)) w2); its
+    mixer is attention over a compressed latent inside a sliding window (a layer may read the latent that an earlier
+    layer keeps) or grouped-query attention with normalised queries and keys, a rotation of neighbouring pairs with
+    stretched frequencies, chunks and a sink in the softmax; its feed-forward is a mixture of experts whose weights
+    multiply the experts' input, beside a gated shared expert.  Tensors: embed, l<i>.norm1, l<i>.norm2, l<i>.mix.*,
+    l<i>.mlp.*, final.norm, head."""
+    e = config.width
+    layers, order = [], []
+    # a latent's pages are kept as long as the widest window among the layers that read them needs them
+    keep = {}
+    for i, l in enumerate(config.layers):
+        if l.type == "latent_attention":
+            owner = i if l.kv_from is None else l.kv_from
+            keep[owner] = max(keep.get(owner, 0), l.mask_size)
+    for i, l in enumerate(config.layers):
+        if l.type == "latent_attention":
+            position = PartSpec("rope_live", {"rotary_dim": l.rot_dim, "theta": l.rot_base, "pairing": "half"})
+            mixer = PartSpec("latent_attention", {
+                "hidden": e, "heads": l.heads, "head_dim": l.dim, "rot_dim": l.rot_dim, "v_dim": l.vdim,
+                "kv_rank": l.kv_rank, "scale": l.scale, "window": l.mask_size, "eps": config.eps,
+                "borrows": l.kv_from is not None, "keep": keep[i if l.kv_from is None else l.kv_from],
+                "position": position})
+        else:
+            position = PartSpec("rope_live", {"rotary_dim": l.rot_dims, "theta": l.rot_base, "pairing": "neighbours",
+                                              "scaling": l.scaling.to_dict() if l.scaling is not None else None})
+            mixer = PartSpec("normed_attention", {
+                "hidden": e, "heads": l.heads, "kv_heads": l.kv_heads, "head_dim": l.dim, "v_dim": l.vdim,
+                "scale": l.scale, "chunk": l.mask_size, "qk_norm": True, "sink": True, "eps": config.eps,
+                "position": position})
+        norm = PartSpec("rms_after", {"size": e, "eps": config.eps, "alpha": config.alpha, "tensor": ""})
+        parts = {"mixer": mixer, "mixer_norm": norm}
+        names = {"mixer": "mix.", "mixer_norm": "norm1", "feed_forward": "mlp.", "feed_forward_norm": "norm2"}
+        if l.mlp is not None:
+            parts["feed_forward"] = PartSpec("routed_experts", {
+                "hidden": e, "experts": l.mlp.experts, "top": l.mlp.top, "intermediate": l.mlp.ff,
+                "shared_intermediate": l.mlp.shared_ff, "shared_gate": bool(l.mlp.shared_ff), "score": "sigmoid",
+                "renormalize": False})
+        if l.mlp is not None or l.second_norm:
+            parts["feed_forward_norm"] = norm
+        layers.append(BlockSpec(kind="post_norm", prefix=f"l{i}.", parts=parts, names=names))
+        order.append(RunStep(i, cache_from=l.kv_from if l.type == "latent_attention" else None))
+    return ModelSpec(
+        architecture=config.architecture, hidden_size=e, vocab_size=config.vocab, max_positions=config.max_positions,
+        layers=tuple(layers), order=tuple(order),
+        final_norm=PartSpec("rms", {"size": e, "eps": config.eps, "tensor": ""}),
+        embedding_name="embed", final_norm_prefix="final.norm", output_name="head", eos_token_id=config.eos_token_id)
+
+
+register_architecture("Tomodra", TomodraConfig, tomodra_spec)

@@ -97,3 +97,119 @@ AIR_API int air_qkv_prepare(const float* proj, int ld, const float* bias, const 
 }
 
 AIR_API int air_trace_set_attention_prepare(unsigned long long* buffer) { return air::set_trace_here(buffer); }
+
+// The same step for layers that normalise queries and keys per head before they rotate them, and whose rotation may
+// pair neighbours:
+//
+//   q and k heads: x <- x / sqrt(mean(x^2) + eps) * w (w [dk], one for all heads of q, one for all heads of k; absent:
+//   no norm); then the first `rot` elements are rotated, pair j by the angle position * freq[j], where pair j is
+//   (2j, 2j + 1) (pairing 1) or (j, j + rot/2) (pairing 0); cos and sin are multiplied by `magnitude`.  The angle is
+//   the product of the position and a 64-bit frequency, and its cos and sin are taken in 64-bit, once per token.
+//   v is copied.  Pages as above.
+//
+// One block per token, one warp per head of q or k; a lane holds up to QKN_PAIRS pairs of its head.
+namespace air {
+
+constexpr int QKN_PAIRS = 4;      // head sizes up to 64 * QKN_PAIRS
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+qk_normed_prepare_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ q_w,
+                         const float* __restrict__ k_w, float eps, const double* __restrict__ freq, int rot,
+                         int pairing, float magnitude, const int* __restrict__ positions,
+                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks,
+                         TO* __restrict__ q_out, TO* __restrict__ cache, int H, int G, int dk, int dv, int P,
+                         int* status) {
+    __shared__ float cs[128], sn[128];
+    pdl_enter(TR_QK_NORMED_PREPARE);
+    const int t = blockIdx.x;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int pos = positions[t];
+    const float* in = proj + (size_t)t * ld;
+    const int half = rot / 2;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        double s, c;
+        sincos((double)pos * freq[j], &s, &c);
+        cs[j] = (float)c * magnitude;
+        sn[j] = (float)s * magnitude;
+    }
+    const int page = block_table[(size_t)slot * max_blocks + pos / P];
+    TO* kdst = nullptr;
+    TO* vdst = nullptr;
+    if (page < 0) {
+        if (threadIdx.x == 0 && status) atomicExch(status, 2);
+    } else {
+        TO* base = cache + (size_t)page * G * P * (dk + dv);
+        kdst = base + (size_t)(pos % P) * dk;
+        vdst = base + (size_t)G * P * dk + (size_t)(pos % P) * dv;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int pairs = dk / 2;
+    for (int head = warp; head < H + G; head += warps) {
+        const float* x = in + (size_t)head * dk;
+        const float* w = head < H ? q_w : k_w;
+        float a[QKN_PAIRS], b[QKN_PAIRS];
+        int ia[QKN_PAIRS], ib[QKN_PAIRS];
+        float ss = 0.f;
+#pragma unroll
+        for (int c = 0; c < QKN_PAIRS; ++c) {
+            const int j = lane + 32 * c;
+            a[c] = b[c] = 0.f;
+            ia[c] = ib[c] = 0;
+            if (j < pairs) {
+                ia[c] = (pairing == 0 && j < half) ? j : 2 * j;
+                ib[c] = (pairing == 0 && j < half) ? j + half : 2 * j + 1;
+                a[c] = x[ia[c]];
+                b[c] = x[ib[c]];
+                ss += a[c] * a[c] + b[c] * b[c];
+            }
+        }
+        ss = warp_sum(ss);
+        const float scale = w ? 1.f / sqrtf(ss / (float)dk + eps) : 1.f;
+        TO* dst = head < H ? q_out + ((size_t)t * H + head) * dk
+                           : (kdst ? kdst + (size_t)(head - H) * P * dk : nullptr);
+#pragma unroll
+        for (int c = 0; c < QKN_PAIRS; ++c) {
+            const int j = lane + 32 * c;
+            if (j >= pairs) continue;
+            float u = a[c], v = b[c];
+            if (w) {
+                u = u * scale * w[ia[c]];
+                v = v * scale * w[ib[c]];
+            }
+            if (j < half) {
+                const float ru = u * cs[j] - v * sn[j], rv = v * cs[j] + u * sn[j];
+                u = ru;
+                v = rv;
+            }
+            if (dst) {
+                dst[ia[c]] = from_float<TO>(u);
+                dst[ib[c]] = from_float<TO>(v);
+            }
+        }
+    }
+    const int vcol = (H + G) * dk;
+    if (vdst)
+        for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x)
+            vdst[(size_t)(idx / dv) * P * dv + idx % dv] = from_float<TO>(in[vcol + idx]);
+}
+
+}  // namespace air
+
+AIR_API int air_qk_normed_prepare(const float* proj, int ld, const float* q_w, const float* k_w, float eps,
+                                  const double* freq, int rot, int pairing, float magnitude, const int* positions,
+                                  const int* token_seq, const int* block_table, int max_blocks, void* q_out,
+                                  void* cache, int out_dtype, int T, int H, int G, int dk, int dv, int P, int* status,
+                                  cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > dk || (rot & 1) || (dk & 1) || rot > 256 || dk > 64 * air::QKN_PAIRS || (rot > 0 && !freq) ||
+        pairing < 0 || pairing > 1 || (!q_w) != (!k_w))
+        return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(out_dtype, TO, return air::launch(air::qk_normed_prepare_kernel<TO>, T, 256, 0, stream, proj, ld, q_w,
+                                                   k_w, eps, freq, rot, pairing, magnitude, positions, token_seq,
+                                                   block_table, max_blocks, (TO*)q_out, (TO*)cache, H, G, dk, dv, P,
+                                                   status));
+    return 0;
+}

@@ -12,7 +12,12 @@
 // q: [T, H, d], out: [T, H, dv].  cache: a page holds the keys [K, P, d] and behind them the values [K, P, dv]
 // (with dv == d that is [page, 2, K, P, d]).  block_table: [slots, max_blocks], row token_seq[t] for token t
 // (negative: padding, skipped).
-// A query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys).
+// A query at position p sees keys max(0, p - window + 1) .. p (window 0: all keys); with mask_mode 1 `window` is the
+// size of a chunk instead, and the query sees the keys p - p % window .. p (those of its own chunk, counted from
+// position 0 of the request).  With `sink` (float32 [H]) the softmax's denominator holds one more term exp(sink[h]),
+// which has no key and no value and is not scaled.  With `latent` a page is [P, d] (one row per token, no heads): every
+// query head reads the same row as its key, and the row's first dv elements as its value.  q is float32 if q_f32,
+// else of the cache's type.
 // score = scale * q.k, and with softcap > 0 then softcap * tanh(score / softcap).  With `gate` [T, H] (float32) a
 // head's output is multiplied by its token's gate.
 #include "common.cuh"
@@ -20,15 +25,15 @@
 namespace air {
 
 constexpr int ATT_WARPS = 4;
-constexpr int ATT_MAX_D = 256;
 
-template <typename T>
+template <typename T, int ATT_MAX_D>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
+paged_attention_ref_kernel(const void* __restrict__ q_any, int q_f32, const T* __restrict__ cache,
                            const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ token_seq, const int* __restrict__ positions,
                            T* __restrict__ out, const float* __restrict__ gate, int H, int K, int d, int dv, int P,
-                           int window, float scale, float softcap) {
+                           int window, float scale, float softcap, int mask_mode, const float* __restrict__ sink,
+                           int latent) {
     __shared__ float sq[ATT_MAX_D];
     __shared__ float sm[ATT_WARPS], sl[ATT_WARPS];
     __shared__ float sacc[ATT_WARPS][ATT_MAX_D];
@@ -39,9 +44,12 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
     const int pos = positions[t];
     const int kvh = (int)(((long long)h * K) / H);
     const int* bt = block_table + (size_t)token_seq[t] * max_blocks;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = window > 0 ? (mask_mode == 1 ? pos - pos % window : max(0, pos - window + 1)) : 0;
 
-    for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = to_float(q[((size_t)t * H + h) * d + i]);
+    if (q_f32)
+        for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = ((const float*)q_any)[((size_t)t * H + h) * d + i];
+    else
+        for (int i = threadIdx.x; i < d; i += blockDim.x) sq[i] = to_float(((const T*)q_any)[((size_t)t * H + h) * d + i]);
     __syncthreads();
 
     const int chunks = (dv + 31) / 32;
@@ -50,8 +58,9 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
     for (int c = 0; c < ATT_MAX_D / 32; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    const size_t page_stride = (size_t)K * P * (d + dv);
-    const size_t v_offset = (size_t)K * P * d;
+    const size_t page_stride = latent ? (size_t)P * d : (size_t)K * P * (d + dv);
+    const size_t v_offset = latent ? 0 : (size_t)K * P * d;
+    const int v_stride = latent ? d : dv;
     for (int b = (lo / 32 / ATT_WARPS) * ATT_WARPS + warp; b * 32 <= pos; b += ATT_WARPS) {
         const int key = b * 32 + lane;
         const bool valid = key >= lo && key <= pos;
@@ -60,7 +69,7 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
         if (valid) {
             const int page = bt[key / P];
             const size_t place = (size_t)kvh * P + (size_t)(key % P);
-            base = (size_t)page * page_stride + v_offset + place * dv;
+            base = (size_t)page * page_stride + v_offset + place * v_stride;
             const T* kp = cache + (size_t)page * page_stride + place * d;
             float dot = 0.f;
             for (int i = 0; i < d; ++i) dot = fmaf(sq[i], to_float(kp[i]), dot);
@@ -95,9 +104,9 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
         if (c < chunks && i < dv) sacc[warp][i] = acc[c];
     }
     __syncthreads();
-    float mm = -INFINITY;
+    float mm = sink ? sink[h] : -INFINITY;
     for (int w = 0; w < ATT_WARPS; ++w) mm = fmaxf(mm, sm[w]);
-    float total = 0.f;
+    float total = sink ? expf(sink[h] - mm) : 0.f;
     float weight[ATT_WARPS];
     for (int w = 0; w < ATT_WARPS; ++w) {
         weight[w] = sm[w] == -INFINITY ? 0.f : expf(sm[w] - mm);
@@ -113,18 +122,24 @@ paged_attention_ref_kernel(const T* __restrict__ q, const T* __restrict__ cache,
 
 }  // namespace air
 
-AIR_API int air_paged_attention_ref(const void* q, const void* cache, int dtype, const int* block_table,
+AIR_API int air_paged_attention_ref(const void* q, int q_f32, const void* cache, int dtype, const int* block_table,
                                     int max_blocks, const int* token_seq, const int* positions, void* out,
                                     const float* gate, int T, int H, int K, int d, int dv, int P, int window,
-                                    float scale, float softcap, cudaStream_t stream) {
+                                    float scale, float softcap, int mask_mode, const float* sink, int latent,
+                                    cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d <= 0 || d > air::ATT_MAX_D || dv <= 0 || dv > air::ATT_MAX_D || H <= 0 || K <= 0 || H > 65535)
+    if (d <= 0 || d > 640 || dv <= 0 || dv > 640 || H <= 0 || K <= 0 || H > 65535 || mask_mode < 0 || mask_mode > 1 ||
+        (latent && (dv > d || K != 1)))
         return AIR_ERR_BAD_ARGUMENT;
     dim3 grid(T, H);
     AIR_DISPATCH(dtype, TT, {
-        return air::launch(air::paged_attention_ref_kernel<TT>, grid, air::ATT_WARPS * 32, 0, stream, (const TT*)q,
+        if (d <= 256 && dv <= 256)
+            return air::launch(air::paged_attention_ref_kernel<TT, 256>, grid, air::ATT_WARPS * 32, 0, stream, q, q_f32,
+                               (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, gate, H, K,
+                               d, dv, P, window, scale, softcap, mask_mode, sink, latent);
+        return air::launch(air::paged_attention_ref_kernel<TT, 640>, grid, air::ATT_WARPS * 32, 0, stream, q, q_f32,
                            (const TT*)cache, block_table, max_blocks, token_seq, positions, (TT*)out, gate, H, K, d,
-                           dv, P, window, scale, softcap);
+                           dv, P, window, scale, softcap, mask_mode, sink, latent);
     });
     return 0;
 }

@@ -1,0 +1,180 @@
+// Matrix products in groups: C_g = A_g W_g^T for many g in one launch, where every group has a matrix W_g [N, K] of its
+// own and a list of rows.  Two users: the experts of a mixture (group = expert, its rows are the tokens that chose it,
+// known only on the device) and products per head (group = head, every group has all the step's rows).
+//
+//   Rows.  A group's rows are consecutive *slots*.  With `start` (device, [G + 1]) group g has the slots start[g] ..
+//   start[g + 1], and `tiles` (device: pairs (group, first slot), their number in num_tiles) says which row tiles
+//   exist; a block whose index is beyond that number leaves.  Without `start` every group has rows_per_group rows
+//   and the grid is (column tiles, row tiles, groups).
+//   Where a slot's row of A lies: with a_index, row a_index[slot] / a_div, times a_scale[a_index[slot]] if a_scale is
+//   given (the product is rounded to A's type, as if a scaled copy of the row had been made); else row `slot`, or
+//   with a_local the row slot - (the group's first slot); plus g * a_group_stride elements.
+//   Where a slot's row of C goes: with o_index, p = o_index[slot]: part p % o_div, row p / o_div of out
+//   [o_div, rows, N] (o_part_stride elements per part); else row `slot` (or, o_local, the row inside the group) plus
+//   g * o_group_stride.
+//   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], rows 0 .. F the gate's and F .. 2 F the
+//   linear branch's; C [rows, F] = silu(gate) * linear in A's type.
+//
+// Arithmetic: 32-bit multiply-adds on the CUDA cores (16-bit operands are widened, so their products are exact), k
+// ascending: a row's result depends on nothing but the row and W_g.  A tile is 64 x 64, a thread holds 4 x 4 of it.
+#include "common.cuh"
+
+namespace air {
+
+struct GroupedArgs {
+    const void* A; long long lda; long long a_group_stride; const int* a_index; int a_div; int a_local;
+    const float* a_scale;
+    const void* W; long long w_group_stride;
+    void* out; long long ldo; long long o_group_stride; const int* o_index; int o_div; long long o_part_stride;
+    int o_local; int out_f32;
+    const int* start; int rows_per_group; const int* tiles; const int* num_tiles;
+    int N, K;
+};
+
+constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 16;
+
+template <typename T, int EPI>
+__global__ void __launch_bounds__(256)
+grouped_gemm_kernel(const GroupedArgs p) {
+    __shared__ float As[GG_BK][GG_BM + 4];
+    __shared__ float Ws[EPI == 1 ? 2 : 1][GG_BK][GG_BN + 4];
+    __shared__ long long a_off[GG_BM], o_off[GG_BM];
+    __shared__ float a_mul[GG_BM];
+    pdl_enter(TR_GROUPED_GEMM);
+    int g, slot0, first, rows;
+    if (p.start) {
+        if ((int)blockIdx.y >= *p.num_tiles) return;
+        g = p.tiles[2 * blockIdx.y];
+        slot0 = p.tiles[2 * blockIdx.y + 1];
+        first = p.start[g];
+        rows = min(GG_BM, p.start[g + 1] - slot0);
+    } else {
+        g = blockIdx.z;
+        first = g * p.rows_per_group;
+        slot0 = first + blockIdx.y * GG_BM;
+        rows = min(GG_BM, p.rows_per_group - (int)blockIdx.y * GG_BM);
+    }
+    if (rows <= 0) return;
+    const int n0 = blockIdx.x * GG_BN;
+    const int tid = threadIdx.x;
+    if (tid < GG_BM) {
+        long long a = -1, o = -1;
+        float mul = 1.f;
+        if (tid < rows) {
+            const int slot = slot0 + tid;
+            if (p.a_index) {
+                const int src = p.a_index[slot];
+                a = (long long)(src / p.a_div) * p.lda + (long long)g * p.a_group_stride;
+                if (p.a_scale) mul = p.a_scale[src];
+            } else {
+                a = (long long)(p.a_local ? slot - first : slot) * p.lda + (long long)g * p.a_group_stride;
+            }
+            if (p.o_index) {
+                const int dst = p.o_index[slot];
+                o = (long long)(dst % p.o_div) * p.o_part_stride + (long long)(dst / p.o_div) * p.ldo;
+            } else {
+                o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
+            }
+        }
+        a_off[tid] = a;
+        o_off[tid] = o;
+        a_mul[tid] = mul;
+    }
+    __syncthreads();
+    const T* A = (const T*)p.A;
+    const T* W = (const T*)p.W + (size_t)g * p.w_group_stride;
+    const int N = p.N, K = p.K;
+    const int lm = tid >> 2, lk = (tid & 3) * 4;      // what this thread loads: row lm, k lk .. lk + 3
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[EPI == 1 ? 2 : 1][4][4];
+#pragma unroll
+    for (int e = 0; e < (EPI == 1 ? 2 : 1); ++e)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[e][i][j] = 0.f;
+    const long long arow = a_off[lm];
+    const float amul = a_mul[lm];
+    const bool scaled = p.a_scale != nullptr;
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            float a = 0.f;
+            if (arow >= 0 && k < K) {
+                a = to_float(A[arow + k]);
+                if (scaled) a = to_float(from_float<T>(a * amul));
+            }
+            As[lk + i][lm] = a;
+#pragma unroll
+            for (int e = 0; e < (EPI == 1 ? 2 : 1); ++e) {
+                const int n = n0 + lm;
+                Ws[e][lk + i][lm] = (n < N && k < K) ? to_float(W[((size_t)e * N + n) * K + k]) : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float a[4], b[EPI == 1 ? 2 : 1][4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int e = 0; e < (EPI == 1 ? 2 : 1); ++e)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[e][j] = Ws[e][kk][tx * 4 + j];
+#pragma unroll
+            for (int e = 0; e < (EPI == 1 ? 2 : 1); ++e)
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc[e][i][j] = fmaf(a[i], b[e][j], acc[e][i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long o = o_off[ty * 4 + i];
+        if (o < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            if (EPI == 1) {
+                const float gate = acc[0][i][j], lin = acc[EPI == 1 ? 1 : 0][i][j];
+                ((T*)p.out)[o + n] = from_float<T>(gate / (1.f + expf(-gate)) * lin);
+            } else if (p.out_f32) {
+                ((float*)p.out)[o + n] = acc[0][i][j];
+            } else {
+                ((T*)p.out)[o + n] = from_float<T>(acc[0][i][j]);
+            }
+        }
+    }
+}
+
+}  // namespace air
+
+AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_stride, const int* a_index, int a_div,
+                             int a_local, const float* a_scale, const void* W, long long w_group_stride, void* out,
+                             long long ldo, long long o_group_stride, const int* o_index, int o_div,
+                             long long o_part_stride, int o_local, int out_f32, const int* start, int rows_per_group,
+                             const int* tiles, const int* num_tiles, int max_tiles, int groups, int N, int K,
+                             int dtype, int epi, cudaStream_t stream) {
+    if (N <= 0 || K <= 0 || groups <= 0) return 0;
+    if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 1 ||
+        (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index))
+        return AIR_ERR_BAD_ARGUMENT;
+    air::GroupedArgs p{A, lda, a_group_stride, a_index, a_div, a_local, a_scale, W, w_group_stride, out, ldo,
+                       o_group_stride, o_index, o_div, o_part_stride, o_local, out_f32, start, rows_per_group, tiles,
+                       num_tiles, N, K};
+    const int row_tiles = start ? max_tiles : (rows_per_group + air::GG_BM - 1) / air::GG_BM;
+    if (row_tiles <= 0) return 0;
+    if (row_tiles > 65535 || groups > 65535) return AIR_ERR_BAD_ARGUMENT;
+    dim3 grid((N + air::GG_BN - 1) / air::GG_BN, row_tiles, start ? 1 : groups);
+    AIR_DISPATCH(dtype, TT, {
+        if (epi == 1) return air::launch(air::grouped_gemm_kernel<TT, 1>, grid, 256, 0, stream, p);
+        return air::launch(air::grouped_gemm_kernel<TT, 0>, grid, 256, 0, stream, p);
+    });
+    return 0;
+}
+
+AIR_API int air_trace_set_grouped_gemm(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -1,0 +1,150 @@
+// Routing of a mixture of experts, on the device from start to end (nothing is read on the host, so a step can be
+// captured in a CUDA graph).
+//
+// moe_route_kernel: from the router's logits z [T, ld] (float32; the first n columns, and at column n, where the
+//   layer has one, the logit of a gate for a shared expert) to each token's `top` experts with the largest scores.
+//   score 0 is sigmoid(z), score 1 the softmax over the n logits; the weights are the chosen scores as they are, or
+//   (renormalize) divided by their sum.  Equal scores: the lower index wins.  One warp per token.
+//   Writes expert [T, top] int32, weight [T, top] float32 and gate [T] = sigmoid(z[n]).
+//
+// moe_sort_kernel: orders the T * top (token, choice) pairs by expert.  Writes start [n + 1] (the slots of expert e are
+//   start[e] .. start[e + 1]), pair_of_slot [T * top] (pair = token * top + choice), and the list of row tiles of
+//   `tile_rows` slots that the grouped matrix product walks: tiles [2 * i] = expert, [2 * i + 1] = first slot, and
+//   their number.  One block.  Inside an expert the order of the slots is whatever the atomic counters give; a row of
+//   a product does not depend on its neighbours, so the result does not depend on it.
+#include "common.cuh"
+
+namespace air {
+
+constexpr int MOE_MAX_PER_LANE = 16;      // up to 512 experts
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ z, int ld, int T, int n, int top, int score, int renormalize,
+                 int has_gate, int* __restrict__ expert, float* __restrict__ weight, float* __restrict__ gate) {
+    pdl_enter(TR_MOE_ROUTE);
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* row = z + (size_t)t * ld;
+    float s[MOE_MAX_PER_LANE];
+    float zmax = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < MOE_MAX_PER_LANE; ++c) {
+        const int e = lane + 32 * c;
+        s[c] = e < n ? row[e] : -INFINITY;
+        zmax = fmaxf(zmax, s[c]);
+    }
+    if (score == 1) {
+        zmax = warp_max(zmax);
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c) {
+            s[c] = lane + 32 * c < n ? expf(s[c] - zmax) : 0.f;
+            sum += s[c];
+        }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c) s[c] /= sum;
+    } else {
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c) s[c] = 1.f / (1.f + expf(-s[c]));
+    }
+#pragma unroll
+    for (int c = 0; c < MOE_MAX_PER_LANE; ++c)
+        if (lane + 32 * c >= n || !(s[c] == s[c])) s[c] = -1.f;      // outside, or not a number: never preferred
+    float total = 0.f;
+    float mine = 0.f;      // lane j keeps the weight of choice j
+    int mine_e = 0;
+    for (int j = 0; j < top; ++j) {
+        float best = -3.f;
+        int best_e = n;
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c) {
+            const int e = lane + 32 * c;
+            if (e < n && s[c] > best) { best = s[c]; best_e = e; }      // ascending e: the first of equals stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+#pragma unroll
+        for (int c = 0; c < MOE_MAX_PER_LANE; ++c)
+            if (lane + 32 * c == best_e) s[c] = -2.f;
+        const float wj = fmaxf(best, 0.f);
+        total += wj;
+        if (lane == (j & 31)) {
+            if (j >= 32) {      // (more than 32 choices: written as they come)
+                expert[(size_t)t * top + j] = best_e;
+                weight[(size_t)t * top + j] = wj;
+            } else {
+                mine = wj;
+                mine_e = best_e;
+            }
+        }
+    }
+    if (lane < top && lane < 32) {
+        expert[(size_t)t * top + lane] = mine_e;
+        weight[(size_t)t * top + lane] = renormalize ? mine / total : mine;
+    }
+    if (gate && lane == 0) gate[t] = has_gate ? 1.f / (1.f + expf(-row[n])) : 1.f;
+}
+
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* __restrict__ expert, int pairs, int n, int tile_rows, int* __restrict__ start,
+                int* __restrict__ pair_of_slot, int* __restrict__ tiles, int* __restrict__ num_tiles) {
+    extern __shared__ int counts[];      // [n] counts, then [n] fill
+    int* fill = counts + n;
+    pdl_enter(TR_MOE_SORT);
+    for (int e = threadIdx.x; e < 2 * n; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = expert[p];
+        if (e >= 0 && e < n) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, nt = 0;
+        for (int e = 0; e < n; ++e) {
+            const int c = counts[e];
+            start[e] = at;
+            fill[e] = at;
+            for (int r = 0; r < c; r += tile_rows) {
+                tiles[2 * nt] = e;
+                tiles[2 * nt + 1] = at + r;
+                ++nt;
+            }
+            at += c;
+        }
+        start[n] = at;
+        *num_tiles = nt;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = expert[p];
+        if (e >= 0 && e < n) pair_of_slot[atomicAdd(&fill[e], 1)] = p;
+    }
+}
+
+}  // namespace air
+
+AIR_API int air_moe_route(const float* z, int ld, int T, int n, int top, int score, int renormalize, int has_gate,
+                          int* expert, float* weight, float* gate, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (n <= 0 || n > 32 * air::MOE_MAX_PER_LANE || top <= 0 || top > n || top > 32 || ld < n + (has_gate ? 1 : 0) ||
+        score < 0 || score > 1)
+        return AIR_ERR_BAD_ARGUMENT;
+    return air::launch(air::moe_route_kernel, (T + 3) / 4, 128, 0, stream, z, ld, T, n, top, score, renormalize,
+                       has_gate, expert, weight, gate);
+}
+
+AIR_API int air_moe_sort(const int* expert, int pairs, int n, int tile_rows, int* start, int* pair_of_slot, int* tiles,
+                         int* num_tiles, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (n <= 0 || n > 4096 || tile_rows <= 0) return AIR_ERR_BAD_ARGUMENT;
+    return air::launch(air::moe_sort_kernel, 1, 1024, sizeof(int) * 2 * (size_t)n, stream, expert, pairs, n, tile_rows,
+                       start, pair_of_slot, tiles, num_tiles);
+}
+
+AIR_API int air_trace_set_moe(unsigned long long* buffer) { return air::set_trace_here(buffer); }

@@ -27,8 +27,22 @@ _SIGNATURES = {
     "air_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "air_convert": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p],
     "air_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "air_paged_attention_ref": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "air_paged_attention_ref": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
+                                c_int, c_void_p],
+    "air_post_norm": [c_void_p, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int,
+                      c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "air_qk_normed_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_float, c_void_p,
+                              c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p, c_void_p],
+    "air_latent_prepare": [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p],
+    "air_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
+                         c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
@@ -95,7 +109,8 @@ def set_pdl(on: bool) -> None:
 TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_mul", 5: "convert", 6: "table_update",
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
                12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
-               17: "qkv_prepare", 18: "glu", 19: "scaled_norm"}
+               17: "qkv_prepare", 18: "glu", 19: "scaled_norm", 20: "post_norm", 21: "qk_normed_prepare",
+               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -308,15 +323,24 @@ def gemm_f32(a, w, bias, out):
 
 
 def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window, scale, softcap=0.0, gate=None,
-                        kv_heads=None, page_tokens=None):
+                        kv_heads=None, page_tokens=None, chunk=None, sink=None, latent=False):
     """Causal attention over the pages with 32-bit arithmetic, for any batch.  q [T, H, d], out [T, H, dv].
     cache [page, 2, K, P, d] where dv == d; where keys and values differ in size a page is flat: the keys
     [K, P, d], then the values [K, P, dv], and kv_heads and page_tokens say what K and P are.  score = scale * q.k,
-    then softcap * tanh(score / softcap) where softcap > 0; gate (float32 [T, H]) multiplies a head's output."""
+    then softcap * tanh(score / softcap) where softcap > 0; gate (float32 [T, H]) multiplies a head's output.
+    Which keys a query at position p sees: all up to its own; with `window` the last `window` of them; with `chunk`
+    those from p - p % chunk on.  sink (float32 [H]): one more term exp(sink[h]) in the softmax's denominator.
+    latent: cache [page, P, d] holds one row per token that every head reads as its key and whose first dv elements
+    it reads as its value; q may then be float32 whatever the cache's type."""
     T, H, d = q.shape
     dv = out.shape[2]
     _req(q, "q", _FLOATS)
-    if cache.dim() == 5:
+    if latent:
+        _req(cache, "cache", (out.dtype,), (None, None, d))
+        K, P = 1, cache.shape[1]
+        if dv > d:
+            raise KernelError("paged_attention_ref: a latent row's value is a part of its key")
+    elif cache.dim() == 5:
         _req(cache, "cache", (q.dtype,), (None, 2, None, None, d))
         K, P = cache.shape[2], cache.shape[3]
         if dv != d:
@@ -326,18 +350,173 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
     else:
         K, P = int(kv_heads), int(page_tokens)
         _req(cache, "cache", (q.dtype,), (None, K * P * (d + dv)))
+    if q.dtype != out.dtype and q.dtype != torch.float32:
+        raise KernelError("paged_attention_ref: q is float32 or of the cache's type")
     _req(block_table, "block_table", _I32)
     _req(token_seq, "token_seq", _I32, (T,))
     _req(positions, "positions", _I32, (T,))
-    _req(out, "out", (q.dtype,), (T, H, dv))
+    _req(out, "out", (cache.dtype,), (T, H, dv))
     if gate is not None:
         _req(gate, "gate", (torch.float32,), (T, H))
-    if d > 256 or dv > 256:
-        raise KernelError(f"head sizes {d} and {dv}: the 32-bit attention kernel takes up to 256")
+    if sink is not None:
+        _req(sink, "sink", (torch.float32,), (H,))
+    if window and chunk:
+        raise KernelError("paged_attention_ref: a window or a chunk, not both")
+    if d > 640 or dv > 640:
+        raise KernelError(f"head sizes {d} and {dv}: the 32-bit attention kernel takes up to 640")
     _check(_get("air_paged_attention_ref")(
-        q.data_ptr(), cache.data_ptr(), _DT[q.dtype], block_table.data_ptr(), block_table.shape[1],
-        token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(gate), T, H, K, d, dv, P,
-        int(window or 0), float(scale), float(softcap or 0.0), _stream()), "paged_attention_ref")
+        q.data_ptr(), 1 if q.dtype == torch.float32 else 0, cache.data_ptr(), _DT[cache.dtype], block_table.data_ptr(),
+        block_table.shape[1], token_seq.data_ptr(), positions.data_ptr(), out.data_ptr(), _ptr(gate), T, H, K, d, dv, P,
+        int(chunk or window or 0), float(scale), float(softcap or 0.0), 1 if chunk else 0, _ptr(sink),
+        1 if latent else 0, _stream()), "paged_attention_ref")
+    return out
+
+
+def post_norm(h, alpha, a, b, b_row_scale, weight, eps, out):
+    """h <- rms(alpha * h + a + s * b) * weight in place (float32), with a copy in out's type (out may be None).
+    a, b: None, float32 [T, E] or partial sums [parts, T, E] added in order; s = b_row_scale (float32 [T]) or 1.
+    weight None: only the sum is written back (no norm)."""
+    T, E = h.shape
+    _req(h, "h", (torch.float32,))
+    parts = []
+    for name, x in (("a", a), ("b", b)):
+        n = 0
+        if x is not None:
+            n = 1 if x.dim() == 2 else x.shape[0]
+            _req(x, name, (torch.float32,), (T, E) if x.dim() == 2 else (n, T, E))
+        parts.append(n)
+    if b_row_scale is not None:
+        _req(b_row_scale, "b_row_scale", (torch.float32,), (T,))
+    if weight is not None:
+        _req(weight, "weight", _FLOATS, (E,))
+    if out is not None:
+        _req(out, "out", _FLOATS, (T, E))
+    _check(_get("air_post_norm")(h.data_ptr(), float(alpha), _ptr(a), parts[0], _ptr(b), parts[1], _ptr(b_row_scale),
+                                 T * E, _ptr(weight), _DT[weight.dtype] if weight is not None else 0, _ptr(out),
+                                 _DT[out.dtype] if out is not None else 0, T, E, float(eps), _stream()), "post_norm")
+    return out
+
+
+def qk_normed_prepare(proj, q_weight, k_weight, eps, freq, pairing, magnitude, positions, token_seq, block_table, q_out,
+                      cache, kv_heads, v_dim, page_tokens, status=None):
+    """From the fused projection proj (float32 [T, (H + G) dk + G dv]: q, k, v per token) to q_out [T, H, dk] and
+    the pages (keys [G, P, dk], then values [G, P, dv]).  q and k heads are normalised (x / sqrt(mean(x^2) + eps) * w,
+    w float32 [dk]: q_weight for q, k_weight for k; None: no norm), then their first 2 * len(freq) elements are
+    rotated by position * freq[j] (freq float64), pair j = (2j, 2j + 1) where pairing == "neighbours", (j, j + rot/2)
+    where "half"; cos and sin are multiplied by magnitude."""
+    T, H, dk = q_out.shape
+    G, dv, P = int(kv_heads), int(v_dim), int(page_tokens)
+    W = (H + G) * dk + G * dv
+    _req(proj, "proj", (torch.float32,), (T, W))
+    for name, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _req(w, name, (torch.float32,), (dk,))
+    rot = 0
+    if freq is not None:
+        _req(freq, "freq", (torch.float64,))
+        rot = 2 * freq.numel()
+    if pairing not in ("half", "neighbours"):
+        raise KernelError(f"qk_normed_prepare: pairing {pairing!r}")
+    _req(positions, "positions", _I32, (T,))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(block_table, "block_table", _I32)
+    _req(q_out, "q_out", _FLOATS)
+    _req(cache, "cache", (q_out.dtype,))
+    if cache[0].numel() != G * P * (dk + dv):
+        raise KernelError(f"qk_normed_prepare: a page of {cache[0].numel()} elements, not {G} x {P} x ({dk} + {dv})")
+    _check(_get("air_qk_normed_prepare")(
+        proj.data_ptr(), W, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(freq), rot,
+        1 if pairing == "neighbours" else 0, float(magnitude), positions.data_ptr(), token_seq.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], q_out.data_ptr(), cache.data_ptr(), _DT[q_out.dtype], T, H, G, dk,
+        dv, P, _ptr(status), _stream()), "qk_normed_prepare")
+    return q_out
+
+
+def latent_prepare(proj, c_weight, eps, freq, positions, token_seq, block_table, q_plain, q_full, cache, owns,
+                   status=None):
+    """From the first projection of a latent-attention layer (float32 [T, H (d + rot) (+ R + rot where owns)]) to
+    q_plain [T, H, d] (the cache's type), the rotated parts in q_full[:, :, R:] (float32 [T, H, R + rot]) and, where
+    owns, the row [rms(c) * c_weight | rotated kr] in the pages (cache [pages, P, R + rot])."""
+    T, H, d = q_plain.shape
+    P, width = cache.shape[1], cache.shape[2]
+    rot = 2 * freq.numel() if freq is not None else 0
+    R = width - rot
+    ld = H * (d + rot) + (width if owns else 0)
+    _req(proj, "proj", (torch.float32,), (T, ld))
+    if freq is not None:
+        _req(freq, "freq", (torch.float64,))
+    if owns:
+        _req(c_weight, "c_weight", (torch.float32,), (R,))
+    _req(positions, "positions", _I32, (T,))
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(block_table, "block_table", _I32)
+    _req(q_plain, "q_plain", _FLOATS)
+    _req(q_full, "q_full", (torch.float32,), (T, H, width))
+    _req(cache, "cache", (q_plain.dtype,))
+    _check(_get("air_latent_prepare")(
+        proj.data_ptr(), ld, _ptr(c_weight), float(eps), _ptr(freq), positions.data_ptr(), token_seq.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], q_plain.data_ptr(), q_full.data_ptr(), cache.data_ptr(),
+        _DT[q_plain.dtype], 1 if owns else 0, T, H, d, rot, R, P, _ptr(status), _stream()), "latent_prepare")
+
+
+def moe_route(z, experts, top, expert_out, weight_out, gate_out=None, has_gate=False, score="sigmoid",
+              renormalize=False):
+    """z float32 [T, >= experts (+ 1)]: router logits.  expert_out int32 [T, top], weight_out float32 [T, top]: the
+    experts with the largest scores (sigmoid(z), or softmax(z)) and those scores (divided by their sum where
+    renormalize); gate_out float32 [T] = sigmoid(z[:, experts]) where has_gate, else 1."""
+    T = z.shape[0]
+    _req(z, "z", (torch.float32,))
+    _req(expert_out, "expert_out", _I32, (T, top))
+    _req(weight_out, "weight_out", (torch.float32,), (T, top))
+    if gate_out is not None:
+        _req(gate_out, "gate_out", (torch.float32,), (T,))
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route: score {score!r}")
+    _check(_get("air_moe_route")(z.data_ptr(), z.shape[1], T, int(experts), int(top), 1 if score == "softmax" else 0,
+                                 1 if renormalize else 0, 1 if has_gate else 0, expert_out.data_ptr(),
+                                 weight_out.data_ptr(), _ptr(gate_out), _stream()), "moe_route")
+
+
+GROUP_TILE = 64      # rows of a tile of the grouped product
+
+
+def moe_sort(expert, experts, start, pair_of_slot, tiles, num_tiles):
+    """Orders the (token, choice) pairs of expert int32 [T, top] by expert: start int32 [experts + 1], pair_of_slot
+    int32 [T * top], the grouped product's row tiles (tiles int32 [max_tiles, 2], num_tiles int32 [1])."""
+    pairs = expert.numel()
+    _req(expert, "expert", _I32)
+    _req(start, "start", _I32, (experts + 1,))
+    _req(pair_of_slot, "pair_of_slot", _I32, (pairs,))
+    _req(tiles, "tiles", _I32, (None, 2))
+    if tiles.shape[0] < pairs // GROUP_TILE + experts:
+        raise KernelError("moe_sort: the tile list is too short")
+    _req(num_tiles, "num_tiles", _I32, (1,))
+    _check(_get("air_moe_sort")(expert.data_ptr(), pairs, int(experts), GROUP_TILE, start.data_ptr(),
+                                pair_of_slot.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), _stream()), "moe_sort")
+
+
+def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group_stride=0, a_index=None, a_div=1,
+                 a_scale=None, a_local=False, o_index=None, o_div=1, o_part_stride=0, o_local=False, start=None,
+                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False):
+    """out rows = a rows @ w[g]^T for every group g (w [groups, n (2n with silu_mul), k]); see grouped_gemm.cu for how
+    rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear."""
+    _req(a, "a", _FLOATS)
+    _req(w, "w", (a.dtype,), (groups, 2 * n if silu_mul else n, k))
+    _req(out, "out", (torch.float32, a.dtype))
+    if silu_mul and out.dtype != a.dtype:
+        raise KernelError("grouped_gemm: the activation is written in the input's type")
+    for name, x in (("a_index", a_index), ("o_index", o_index), ("start", start), ("tiles", tiles),
+                    ("num_tiles", num_tiles)):
+        if x is not None:
+            _req(x, name, _I32)
+    if a_scale is not None:
+        _req(a_scale, "a_scale", (torch.float32,))
+    _check(_get("air_grouped_gemm")(
+        a.data_ptr(), int(lda), int(a_group_stride), _ptr(a_index), int(a_div), 1 if a_local else 0, _ptr(a_scale),
+        w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), int(ldo), int(o_group_stride), _ptr(o_index), int(o_div),
+        int(o_part_stride), 1 if o_local else 0, 1 if out.dtype == torch.float32 else 0, _ptr(start),
+        int(rows_per_group), _ptr(tiles), _ptr(num_tiles), tiles.shape[0] if tiles is not None else 0, int(groups),
+        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, _stream()), "grouped_gemm")
     return out
 
 

@@ -1,7 +1,8 @@
 from .spec import PartSpec, BlockSpec, ModelSpec, RunStep
-from .base import (Runtime, CacheNeed, PagedKV, PagedKVView, SlotState, SlotStateView, HostBatch, Plan, ScaledSum, Part, Mixer,
+from .base import (Runtime, CacheNeed, PagedKV, PagedKVView, PagedLatent, PagedLatentView, GatedSum, SlotState, SlotStateView, HostBatch, Plan, ScaledSum, Part, Mixer,
                    FeedForward, Norm, PositionEncoding)
 from .registry import (register_mixer, register_feed_forward, register_norm, register_position_encoding,
                        register_block, register_architecture, architecture, architectures)
-from . import norm, rope, attention, capped_attention, recurrent, mlp, block  # registers the parts that ship with the engine
+from . import (norm, rope, attention, capped_attention, recurrent, mlp, block, normed_attention, latent_attention,
+               experts)  # registers the parts that ship with the engine
 from .block import Block

@@ -63,9 +63,20 @@ class CacheNeed:
     keeps `slot_shape()` per request, zeroed when the request opens."""
     paged: bool = False
     window: Optional[int] = None
+    chunk: Optional[int] = None
 
     def group_key(self) -> Hashable:
         return self
+
+    def first_live(self, length: int) -> int:
+        """The lowest position that a query at position `length` or later can still see: pages that hold only
+        earlier tokens go back to the pool.  A window keeps the last `window` keys; chunks (a query sees the keys of
+        its own chunk of `chunk` positions, counted from 0) keep the chunk that position `length` lies in."""
+        if self.window is not None:
+            return max(0, length - self.window + 1)
+        if self.chunk is not None:
+            return length - length % self.chunk
+        return 0
 
     def page_shape(self, page_tokens: int) -> Tuple[int, ...]:
         raise NotImplementedError
@@ -114,6 +125,7 @@ class PagedKV(CacheNeed):
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None
+    chunk: Optional[int] = None
     paged = True
 
     def page_shape(self, page_tokens):
@@ -123,6 +135,30 @@ class PagedKV(CacheNeed):
 
     def view(self, tensor, group):
         return PagedKVView(tensor, group, self)
+
+
+@dataclass
+class PagedLatentView:
+    """What a mixer gets for a PagedLatent need: its slab [pages, page_tokens, width] and the index of its group."""
+    rows: Optional[torch.Tensor]
+    group: int
+    need: "PagedLatent"
+
+
+@dataclass(frozen=True)
+class PagedLatent(CacheNeed):
+    """One row of `width` numbers per token, in pages [page_tokens, width], with no heads: what attention over a
+    compressed latent keeps (the latent and a rotated key part that all heads share).  window as for PagedKV: the
+    largest window of the layers that read the rows, None if one of them sees everything."""
+    width: int
+    window: Optional[int] = None
+    paged = True
+
+    def page_shape(self, page_tokens):
+        return (page_tokens, self.width)
+
+    def view(self, tensor, group):
+        return PagedLatentView(tensor, group, self)
 
 
 @dataclass(frozen=True)
@@ -198,6 +234,16 @@ class ScaledSum:
     terms: list
 
 
+@dataclass
+class GatedSum:
+    """a + gate[row] * b: what a feed-forward adds to the stream when one of its branches carries a gate of one number
+    per token.  a, b: None, float32 [T, hidden] or partial sums [parts, T, hidden]; gate: float32 [T] or None (1).  A
+    form of a norm's `delta`."""
+    a: Optional[torch.Tensor]
+    b: Optional[torch.Tensor]
+    gate: Optional[torch.Tensor]
+
+
 class Part:
     # True if forward() only launches work on the current stream from device data (no host
     # reads of the batch or of a result), so that a decode step can be captured in a CUDA graph.
@@ -238,6 +284,8 @@ class Norm(Part):
             from ..csrc import ops
             if isinstance(delta, ScaledSum):
                 ops.scaled_norm(h, delta.terms, None, 0.0, None)
+            elif isinstance(delta, GatedSum):
+                ops.post_norm(h, 1.0, delta.a, delta.b, delta.gate, None, 0.0, None)
             else:
                 ops.add_parts(h, delta)
         return h

@@ -133,3 +133,54 @@ class ParallelBlock(Block):
         if self.feed_forward is not None:
             terms.append((self.feed_forward.forward(x, ctx), self.scales.get("feed_forward")))
         return h, ScaledSum(terms)
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """h = norm1(alpha h + mixer(h)); h = norm2(alpha h + feed_forward(h)): the norm stands behind the sum, so the
+    stream itself is normalised and the sub-layers read it as it is.  Roles: mixer, mixer_norm, and optionally
+    feed_forward and feed_forward_norm (a layer without feed-forward may still have the second norm); the norms are of
+    a kind that replaces the stream (rms_after), and alpha is their parameter.
+
+    The stream h is float32.  The rows that the matrix products read (the same numbers in the compute dtype) are written
+    by the norm's kernel and handed from block to block in ctx.shared."""
+
+    ROWS = "post_norm.rows"
+
+    def __init__(self, spec: BlockSpec):
+        super().__init__(spec)
+        self.mixer = MIXERS.get(spec.part("mixer").kind)(spec.part("mixer"), spec.name("mixer"))
+        self.mixer_norm = NORMS.get(spec.part("mixer_norm").kind)(spec.part("mixer_norm"), spec.name("mixer_norm"))
+        self.feed_forward = self.ff_norm = None
+        if "feed_forward" in spec.parts:
+            self.feed_forward = FEED_FORWARDS.get(spec.part("feed_forward").kind)(spec.part("feed_forward"),
+                                                                                  spec.name("feed_forward"))
+        if "feed_forward_norm" in spec.parts:
+            self.ff_norm = NORMS.get(spec.part("feed_forward_norm").kind)(spec.part("feed_forward_norm"),
+                                                                          spec.name("feed_forward_norm"))
+        if self.feed_forward is not None and self.ff_norm is None:
+            raise ValueError(f"block 'post_norm' at '{spec.prefix}': a feed-forward needs the norm behind it")
+
+    def parts(self):
+        return tuple(p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ff_norm) if p is not None)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def forward(self, h, pending, ctx, cache, owns_cache=True):
+        import torch
+        from ..csrc import ops
+        from .base import Norm
+        ctx.residual = None
+        x = ctx.shared.pop(self.ROWS, None)
+        if pending is not None:
+            Norm.add_delta(h, pending)
+            x = None
+        if x is None:
+            rt = self.mixer.rt
+            x = h if rt.is_fp32 else ops.convert(h, torch.empty(h.shape, dtype=rt.dtype, device=h.device))
+        x = self.mixer_norm.forward(h, self.mixer.forward(x, ctx, cache, owns_cache))
+        if self.ff_norm is not None:
+            x = self.ff_norm.forward(h, self.feed_forward.forward(x, ctx) if self.feed_forward is not None else None)
+        ctx.shared[self.ROWS] = x
+        return h, None

@@ -1,0 +1,107 @@
+"""A mixture of gated experts with a router on the device, beside an optional shared expert."""
+from __future__ import annotations
+
+import torch
+
+from ..config.model_config import ConfigError
+from ..csrc import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward, GatedSum
+from .linear import Linear
+from .mlp import SwiGLU
+from .registry import register_feed_forward
+from .spec import PartSpec
+
+
+@register_feed_forward("swiglu_plain_names")
+class PlainNamesSwiGLU(SwiGLU):
+    """SwiGLU whose three matrices are called <prefix>gate, up and down."""
+    NAMES = {"gate": "gate", "up": "up", "down": "down"}
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(FeedForward):
+    """y = sum over the token's `top` experts e of expert_e(s_e x)  +  g shared(x).
+
+    Router: z = Wr x in 32-bit; scores s = sigmoid(z) (score "sigmoid") or softmax(z); the `top` largest are chosen
+    (of equal scores the lower index); the weights are the chosen scores, divided by their sum where renormalize.  The
+    weight multiplies the expert's INPUT (the scaled row is rounded to the compute dtype like any input of a product),
+    which is not the same as weighting its output, since an expert is not linear.  expert(u) = Wdown (silu(Wgate u) *
+    (Wup u)).  The shared expert (shared_intermediate > 0) has the same form and runs for every token; with shared_gate
+    its output is multiplied by g = sigmoid(w_sg . x), one number per token, else g = 1.
+
+    params: hidden, experts, top, intermediate, shared_intermediate, shared_gate, score, renormalize.
+    Tensors: <prefix>router [experts, hidden], e<i>.gate, e<i>.up [intermediate, hidden], e<i>.down [hidden,
+    intermediate], shared.gate, shared.up, shared.down, shared.sg [1, hidden].
+
+    Everything happens on the device: a kernel picks the experts, one orders the (token, choice) pairs by expert, and
+    two grouped products (gate and up with the activation; down) walk the experts' rows.  The outputs of a token's
+    choices land in `top` planes that the norm behind the layer adds in order, so the sum does not depend on the
+    batch."""
+
+    graph_safe = True
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.experts, self.top = p["hidden"], p["experts"], p["top"]
+        self.inter, self.shared_inter = p["intermediate"], int(p.get("shared_intermediate") or 0)
+        self.shared_gate = bool(p.get("shared_gate", False)) and self.shared_inter > 0
+        self.score, self.renormalize = p.get("score", "sigmoid"), bool(p.get("renormalize", False))
+        if self.experts > 512 or self.top > 32:
+            raise ConfigError("unsupported", "routed experts: up to 512 experts and 32 choices per token")
+        self.shared = None
+        if self.shared_inter:
+            self.shared = PlainNamesSwiGLU(PartSpec("swiglu_plain_names", {"hidden": self.hidden,
+                                                                           "intermediate": self.shared_inter}),
+                                           prefix + "shared.")
+
+    def tensor_specs(self):
+        p, e, f = self.prefix, self.hidden, self.inter
+        specs = [TensorSpec(p + "router", (self.experts, e), wide=True)]
+        for i in range(self.experts):
+            specs += [TensorSpec(f"{p}e{i}.gate", (f, e)), TensorSpec(f"{p}e{i}.up", (f, e)),
+                      TensorSpec(f"{p}e{i}.down", (e, f))]
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        if self.shared_gate:
+            specs.append(TensorSpec(p + "shared.sg", (1, e), wide=True))
+        return specs
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        p, n = self.prefix, self.experts
+        rows = [tensors[p + "router"]] + ([tensors[p + "shared.sg"]] if self.shared_gate else [])
+        # the router and the shared expert's gate are one 32-bit product on the CUDA cores
+        self.router = Linear(torch.cat([r.to(torch.float32) for r in rows], dim=0).contiguous(), rt.status)
+        self.gate_up = torch.stack([torch.cat([tensors[f"{p}e{i}.gate"], tensors[f"{p}e{i}.up"]], dim=0)
+                                    for i in range(n)]).contiguous()             # [n, 2F, E]
+        self.down = torch.stack([tensors[f"{p}e{i}.down"] for i in range(n)]).contiguous()      # [n, E, F]
+        if self.gate_up.dtype != rt.dtype:
+            raise ValueError(f"{p}: the experts are stored as {self.gate_up.dtype}, the engine computes in {rt.dtype}")
+        if self.shared is not None:
+            self.shared.load(tensors, rt)
+
+    def forward(self, x, ctx):
+        T, E, F, n, top = x.shape[0], self.hidden, self.inter, self.experts, self.top
+        dev = x.device
+        z = self.router(x, torch.float32)
+        expert = torch.empty((T, top), dtype=torch.int32, device=dev)
+        weight = torch.empty((T, top), dtype=torch.float32, device=dev)
+        gate = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
+        ops.moe_route(z, n, top, expert, weight, gate, has_gate=self.shared_gate, score=self.score,
+                      renormalize=self.renormalize)
+        pairs = T * top
+        ints = torch.empty(n + 1 + pairs + 2 * (pairs // ops.GROUP_TILE + n) + 1, dtype=torch.int32, device=dev)
+        start, pair_of_slot = ints[:n + 1], ints[n + 1:n + 1 + pairs]
+        tiles, num_tiles = ints[n + 1 + pairs:-1].view(-1, 2), ints[-1:]
+        ops.moe_sort(expert, n, start, pair_of_slot, tiles, num_tiles)
+        act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
+        ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
+                         a_scale=weight.view(-1), start=start, tiles=tiles, num_tiles=num_tiles, silu_mul=True)
+        y = torch.empty((top, T, E), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(act, self.down, y, E, F, lda=F, ldo=E, groups=n, o_index=pair_of_slot, o_div=top,
+                         o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles)
+        if self.shared is None:
+            return y
+        return GatedSum(y, self.shared.forward(x, ctx), gate)

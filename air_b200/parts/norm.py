@@ -5,7 +5,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, PreNormed, ScaledSum
+from .base import GatedSum, Norm, PreNormed, ScaledSum
 from .registry import register_norm
 
 
@@ -49,3 +49,34 @@ class RMSNorm(Norm):
         ss = torch.empty((-(-E // ops.PRENORM_CHUNK), T), dtype=torch.float32, device=h.device)
         ops.add_prenorm(h, delta, self.weight, xg, ss)
         return PreNormed(xg, ss, self.eps)
+
+
+@register_norm("rms_after")
+class PostRMSNorm(Norm):
+    """The norm of a layer that normalises after the sum: the stream itself becomes rms(alpha * h + delta) * w, with
+    rms(x) = x / sqrt(mean(x^2) + eps).  params: size, eps, alpha; tensor: what follows the prefix in the weight's name.
+    forward() replaces h in place (float32) and returns the same rows in the compute dtype (h itself in a float32
+    engine).  delta: None, a tensor, partial sums, or a GatedSum; everything is summed in 32-bit."""
+
+    graph_safe = True
+
+    def tensor_specs(self):
+        return [TensorSpec(self.prefix + self.spec.get("tensor", "weight"), (self.spec["size"],),
+                           init="one_plus_normal", wide=True)]
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        self.weight = tensors[self.prefix + self.spec.get("tensor", "weight")]
+        self.eps, self.alpha = float(self.spec["eps"]), float(self.spec["alpha"])
+
+    def forward(self, h, delta, rows=None):
+        if rows is not None:
+            raise ops.KernelError("rms_after replaces the whole stream: it takes no rows")
+        if isinstance(delta, ScaledSum):
+            raise ops.KernelError("rms_after: sums with a scale per column are not offered")
+        a, b, gate = (delta.a, delta.b, delta.gate) if isinstance(delta, GatedSum) else (delta, None, None)
+        if a is not None and a.dtype != torch.float32:
+            a = ops.convert(a, torch.empty(a.shape, dtype=torch.float32, device=a.device))
+        out = None if self.rt.is_fp32 else torch.empty(h.shape, dtype=self.rt.dtype, device=h.device)
+        ops.post_norm(h, self.alpha, a, b, gate, self.weight, self.eps, out)
+        return h if out is None else out

@@ -1,0 +1,109 @@
+"""Grouped-query attention with normalised queries and keys, chunks or a window, and a sink in the softmax."""
+from __future__ import annotations
+
+import torch
+
+from ..config.model_config import ConfigError
+from ..csrc import ops
+from ..weights.loader import TensorSpec
+from .base import Mixer, PagedKV
+from .linear import Linear
+from .registry import register_mixer, POSITION_ENCODINGS
+
+
+@register_mixer("normed_attention")
+class NormedAttention(Mixer):
+    """Causal softmax attention over the paged cache in which
+
+      * keys and queries have one size per head (head_dim) and values another (v_dim); query head h reads key/value
+        head h // (heads / kv_heads);
+      * with qk_norm every head of q and of k is normalised before it is rotated: x / sqrt(mean(x^2) + eps) * w, one
+        weight [head_dim] for all heads of q and one for all heads of k;
+      * the position encoding (kind rope_live) rotates the first part of a head, in halves or in neighbouring pairs,
+        with frequencies that may be stretched, and a magnitude on cos and sin;
+      * the score is scale * q.k with `scale` given;
+      * a query sees the keys up to its own: all of them, the last `window` of them, or (chunk) those of its own
+        chunk, the chunks counted from position 0 of the request whatever the portions a prompt came in;
+      * with sink the softmax's denominator has one more term exp(sink_h), a learned number per head that has no key
+        and no value.
+
+    params: hidden, heads, kv_heads, head_dim, v_dim, scale, window, chunk (at most one of the two), qk_norm, sink, eps,
+    position.  Tensors: <prefix>q [heads*head_dim, hidden], k [kv_heads*head_dim, hidden], v [kv_heads*v_dim, hidden],
+    q.norm, k.norm [head_dim] where qk_norm, sink [heads] where sink, o [hidden, heads*v_dim].
+
+    q, k and v are one product; one kernel then normalises, rotates and writes keys and values to the pages; pages of a
+    chunk that no later query can see go back to the pool."""
+
+    graph_safe = True
+
+    def __init__(self, spec, prefix=""):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.hidden, self.heads, self.kv_heads = p["hidden"], p["heads"], p["kv_heads"]
+        self.head_dim, self.v_dim = p["head_dim"], p.get("v_dim") or p["head_dim"]
+        self.scale, self.eps = float(p["scale"]), float(p.get("eps", 1e-6))
+        self.window, self.chunk = p.get("window"), p.get("chunk")
+        self.qk_norm, self.sink = bool(p.get("qk_norm", False)), bool(p.get("sink", False))
+        if self.window and self.chunk:
+            raise ConfigError("data_error", "normed_attention: a window or chunks, not both")
+        if self.heads % self.kv_heads:
+            raise ConfigError("data_error", "attention: heads must be a multiple of kv_heads")
+        if self.head_dim % 2 or max(self.head_dim, self.v_dim) > 256:
+            raise ConfigError("unsupported", f"attention: head sizes {self.head_dim} / {self.v_dim}: the kernels take "
+                                             "even key sizes, and sizes up to 256")
+        pos = p["position"]
+        self.position = POSITION_ENCODINGS.get(pos.kind)(pos)
+
+    def cache_needs(self):
+        return (PagedKV(self.kv_heads, self.head_dim, self.window, self.v_dim, self.chunk),)
+
+    def tensor_specs(self):
+        p, e = self.prefix, self.hidden
+        specs = [TensorSpec(p + "q", (self.heads * self.head_dim, e)),
+                 TensorSpec(p + "k", (self.kv_heads * self.head_dim, e)),
+                 TensorSpec(p + "v", (self.kv_heads * self.v_dim, e))]
+        if self.qk_norm:
+            specs += [TensorSpec(p + n + ".norm", (self.head_dim,), init="one_plus_normal", wide=True) for n in "qk"]
+        if self.sink:
+            specs.append(TensorSpec(p + "sink", (self.heads,), std=1.0, wide=True))
+        specs.append(TensorSpec(p + "o", (e, self.heads * self.v_dim)))
+        return specs + self.position.tensor_specs()
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        p = self.prefix
+        ws = [tensors[p + n] for n in "qkv"]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError(f"{p}: the projections are stored in different precisions")
+        self.proj = Linear(torch.cat(ws, dim=0).contiguous(), rt.status)
+        self.o = Linear(tensors[p + "o"], rt.status)
+        self.q_weight = self.k_weight = self.sinks = None
+        if self.qk_norm:
+            self.q_weight = tensors[p + "q.norm"].to(torch.float32).contiguous()
+            self.k_weight = tensors[p + "k.norm"].to(torch.float32).contiguous()
+        if self.sink:
+            self.sinks = tensors[p + "sink"].to(torch.float32).contiguous()
+        self.position.load(tensors, rt)
+        if not hasattr(self.position, "frequencies64"):
+            raise ConfigError("unsupported", "normed_attention takes a position encoding that gives 64-bit frequencies")
+        if self.position.rotary_dim > self.head_dim:
+            raise ConfigError("data_error", "normed_attention: the rotated part is larger than a head")
+
+    def forward(self, x, ctx, cache, owns_cache=True):
+        if not owns_cache:
+            raise ops.KernelError("normed_attention: a run that reads another run's keys and values is not offered")
+        (pages,) = cache
+        T, H, G, dk, dv = x.shape[0], self.heads, self.kv_heads, self.head_dim, self.v_dim
+        rt = self.rt
+        P = rt.page_tokens
+        proj = self.proj.f32(x)
+        q = torch.empty((T, H, dk), dtype=rt.dtype, device=x.device)
+        bt = ctx.block_tables[pages.group]
+        kv = pages.kv.view(pages.kv.shape[0], -1)
+        pos = self.position
+        ops.qk_normed_prepare(proj, self.q_weight, self.k_weight, self.eps, pos.frequencies64(), pos.pairing,
+                              pos.magnitude, ctx.positions, ctx.token_seq, bt, q, kv, G, dv, P, status=ctx.status)
+        out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
+        ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale, kv_heads=G,
+                                page_tokens=P, chunk=self.chunk, sink=self.sinks)
+        return self.o.f32_sums(out.view(T, H * dv))

@@ -66,3 +66,58 @@ class RopeHalfLive(PositionEncoding):
 @register_position_encoding("none")
 class NoPosition(PositionEncoding):
     """No position encoding: the mixer's kernel rotates nothing."""
+
+
+def bent_frequencies(rot: int, theta: float, scaling=None):
+    """(float64 frequencies [rot / 2], what cos and sin are multiplied by) of a rotation whose slow pairs are
+    stretched for contexts longer than the model was trained on (the YaRN rule).  scaling: None, or a mapping with
+    factor, original (the trained length), fast and slow (turns over the trained length above which a pair is left
+    alone, and below which it is divided by factor).  With pair(t) = rot ln(original / (2 pi t)) / (2 ln theta),
+    lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), rot - 1), r_i = clamp((i - lo) / max(hi - lo, 0.001),
+    0, 1): frequency i = f_i / factor * r_i + f_i (1 - r_i); the magnitude is 0.1 ln(factor) + 1."""
+    import math
+    i = torch.arange(rot // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / max(rot, 1))
+    if not scaling:
+        return f, 1.0
+    factor, original = float(scaling["factor"]), float(scaling["original"])
+
+    def pair(turns):
+        return rot * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(float(theta)))
+
+    lo = max(math.floor(pair(float(scaling["fast"]))), 0)
+    hi = min(math.ceil(pair(float(scaling["slow"]))), rot - 1)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return f / factor * ramp + f * (1.0 - ramp), 0.1 * math.log(factor) + 1.0
+
+
+@register_position_encoding("rope_live")
+class RopeLive(PositionEncoding):
+    """A rotation of the first rotary_dim elements of a head without a table: the mixer's kernel takes the angle
+    position * frequency in 64-bit and its cos and sin once per token.  params: rotary_dim, theta, pairing ("half":
+    element i with i + rotary_dim / 2; "neighbours": element 2i with 2i + 1), scaling (None or the mapping that
+    bent_frequencies describes).  frequencies64(): float64 [rotary_dim / 2] on the device; magnitude: what cos and sin
+    are multiplied by."""
+
+    def load(self, tensors, rt):
+        super().load(tensors, rt)
+        rot, theta = int(self.spec["rotary_dim"]), float(self.spec["theta"])
+        self.pairing = self.spec.get("pairing", "half")
+        scaling = self.spec.get("scaling")
+        if rot % 2 or rot < 0:
+            raise ValueError("rope_live needs an even rotary width")
+        if self.pairing not in ("half", "neighbours"):
+            raise ValueError(f"rope_live: pairing {self.pairing!r}")
+        self.rotary_dim = rot
+        key = ("rope_live", rot, theta, tuple(sorted(scaling.items())) if scaling else None)
+        made = rt.shared.get(key)
+        if made is None:
+            f, magnitude = bent_frequencies(rot, theta, scaling)
+            made = rt.shared[key] = (f.to(rt.device), float(magnitude))
+        self._frequencies64, self.magnitude = made
+
+    def frequencies64(self):
+        return self._frequencies64 if self.rotary_dim else None
+
+    def frequencies(self):
+        return self._frequencies64.to(torch.float32) if self.rotary_dim else None
