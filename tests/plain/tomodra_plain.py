@@ -190,10 +190,14 @@ def expert(u, w, p):
     return (silu(u @ w[p + "gate"].T) * (u @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def mixture(x, w, p, f):
+def mixture(x, w, p, f, margins=None):
+    """margins (a list) receives, per token, by how much the last chosen score beats the best one left out."""
     n, top = int(f["router"]["experts"]), int(f["router"]["top"])
     s = sigmoid(x @ w[p + "router"].T)                            # [T, n]
     chosen = np.argsort(-s, axis=-1, kind="stable")[:, :top]
+    if margins is not None:
+        ranked = -np.sort(-s, axis=-1)
+        margins.append(ranked[:, top - 1] - ranked[:, top] if top < n else np.full(len(x), np.inf))
     y = np.zeros_like(x)
     for e in range(n):
         for t in np.nonzero((chosen == e).any(axis=-1))[0]:
@@ -204,8 +208,9 @@ def mixture(x, w, p, f):
 
 
 # ----------------------------------------------------------------------------- the model
-def forward(config, weights, tokens, dtype=np.float64, layers_out=None):
-    """Logits [T, vocab] of one sequence; layers_out (a list) receives the stream after every layer."""
+def forward(config, weights, tokens, dtype=np.float64, layers_out=None, margins=None):
+    """Logits [T, vocab] of one sequence; layers_out (a list) receives the stream after every layer, margins (a list)
+    the routers' margins per token, one array per layer with a feed-forward."""
     w = {k: (v.astype(dtype) if v.dtype.kind == "f" else v) for k, v in weights.items()}
     eps, alpha = float(config["norm"]["eps"]), float(config["postln_alpha"])
     tokens = np.asarray(tokens)
@@ -226,7 +231,9 @@ def forward(config, weights, tokens, dtype=np.float64, layers_out=None):
             raise ValueError(layer["type"])
         x = rms_norm(alpha * x + y, w[f"l{i}.norm1"], eps)
         if layer.get("mlp") is not None:
-            x = rms_norm(alpha * x + mixture(x, w, f"l{i}.mlp.", layer["mlp"]), w[f"l{i}.norm2"], eps)
+            x = rms_norm(alpha * x + mixture(x, w, f"l{i}.mlp.", layer["mlp"], margins), w[f"l{i}.norm2"], eps)
+        elif f"l{i}.norm2" in w:
+            x = rms_norm(alpha * x, w[f"l{i}.norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
