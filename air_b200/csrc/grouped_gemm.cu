@@ -15,9 +15,13 @@
 //   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], rows 0 .. F the gate's and F .. 2 F the
 //   linear branch's; C [rows, F] = silu(gate) * linear in A's type.
 //
-// Arithmetic: 32-bit multiply-adds on the CUDA cores (16-bit operands are widened, so their products are exact), k
-// ascending: a row's result depends on nothing but the row and W_g.  A tile is 64 x 64, a thread holds 4 x 4 of it.
+// Arithmetic.  float32 operands (and bfloat16 ones whose strides are not multiples of 8 elements): 32-bit multiply-adds
+// on the CUDA cores, k ascending; a tile is 64 x 64, a thread holds 4 x 4 of it (grouped_gemm_kernel).  bfloat16
+// operands: the warp-level tensor-core instruction (m16n8k16, 32-bit accumulators), four warps of 16 rows by 64
+// columns each, operands staged through shared memory in steps of 32 of k with the next step's loads in flight
+// (grouped_gemm_tc_kernel).  Either way a row's result depends on nothing but the row and W_g.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace air {
 
@@ -151,6 +155,150 @@ grouped_gemm_kernel(const GroupedArgs p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------- bfloat16, tensor cores
+constexpr int GT_BK = 32, GT_LD = GT_BK + 8;      // a row of a staged tile: 32 elements and 16 bytes of padding
+
+template <int EPI>
+__global__ void __launch_bounds__(128)
+grouped_gemm_tc_kernel(const GroupedArgs p) {
+    constexpr int NW = EPI == 1 ? 2 : 1;
+    __shared__ __align__(16) __nv_bfloat16 As[GG_BM][GT_LD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[NW][GG_BN][GT_LD];
+    __shared__ long long a_off[GG_BM], o_off[GG_BM];
+    __shared__ float a_mul[GG_BM];
+    pdl_enter(TR_GROUPED_GEMM);
+    int g, slot0, first, rows;
+    if (p.start) {
+        if ((int)blockIdx.y >= *p.num_tiles) return;
+        g = p.tiles[2 * blockIdx.y];
+        slot0 = p.tiles[2 * blockIdx.y + 1];
+        first = p.start[g];
+        rows = min(GG_BM, p.start[g + 1] - slot0);
+    } else {
+        g = blockIdx.z;
+        first = g * p.rows_per_group;
+        slot0 = first + blockIdx.y * GG_BM;
+        rows = min(GG_BM, p.rows_per_group - (int)blockIdx.y * GG_BM);
+    }
+    if (rows <= 0) return;
+    const int n0 = blockIdx.x * GG_BN;
+    const int tid = threadIdx.x;
+    if (tid < GG_BM) {
+        long long a = -1, o = -1;
+        float mul = 1.f;
+        if (tid < rows) {
+            const int slot = slot0 + tid;
+            if (p.a_index) {
+                const int src = p.a_index[slot];
+                a = (long long)(src / p.a_div) * p.lda + (long long)g * p.a_group_stride;
+                if (p.a_scale) mul = p.a_scale[src];
+            } else {
+                a = (long long)(p.a_local ? slot - first : slot) * p.lda + (long long)g * p.a_group_stride;
+            }
+            if (p.o_index) {
+                const int dst = p.o_index[slot];
+                o = (long long)(dst % p.o_div) * p.o_part_stride + (long long)(dst / p.o_div) * p.ldo;
+            } else {
+                o = (long long)(p.o_local ? slot - first : slot) * p.ldo + (long long)g * p.o_group_stride;
+            }
+        }
+        a_off[tid] = a;
+        o_off[tid] = o;
+        a_mul[tid] = mul;
+    }
+    __syncthreads();
+    const __nv_bfloat16* A = (const __nv_bfloat16*)p.A;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + (size_t)g * p.w_group_stride;
+    const int N = p.N, K = p.K;
+    const bool scaled = p.a_scale != nullptr;
+    // what this thread stages per step: chunks (16 bytes, 8 of k) c = tid and tid + 128 of the 64 x 4 chunks of a tile
+    uint4 ra[2], rw[NW][2];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int c = tid + 128 * i, row = c >> 2, k = k0 + (c & 3) * 8;
+            const long long arow = a_off[row];
+            ra[i] = (arow >= 0 && k < K) ? ldg16(A + arow + k) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int e = 0; e < NW; ++e) {
+                const int n = n0 + row;
+                rw[e][i] = (n < N && k < K) ? ldg16(W + ((size_t)e * N + n) * K + k) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int c = tid + 128 * i, row = c >> 2, kc = (c & 3) * 8;
+            uint4 v = ra[i];
+            if (scaled) {
+                const float m = a_mul[row];
+                uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&w32[j]);
+                    w32[j] = pack_bf16(__low2float(x) * m, __high2float(x) * m);
+                }
+            }
+            *reinterpret_cast<uint4*>(&As[row][kc]) = v;
+#pragma unroll
+            for (int e = 0; e < NW; ++e) *reinterpret_cast<uint4*>(&Ws[e][row][kc]) = rw[e][i];
+        }
+    };
+    const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+    const int r0 = warp * 16;
+    float acc[NW][8][4];
+#pragma unroll
+    for (int e = 0; e < NW; ++e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[e][j][i] = 0.f;
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += GT_BK) {
+        stage();
+        __syncthreads();
+        if (k0 + GT_BK < K) fetch(k0 + GT_BK);
+#pragma unroll
+        for (int kk = 0; kk < GT_BK; kk += 16) {
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq][kk + 2 * tq]);
+            const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq + 8][kk + 2 * tq]);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq][kk + 2 * tq + 8]);
+            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq + 8][kk + 2 * tq + 8]);
+#pragma unroll
+            for (int e = 0; e < NW; ++e)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[e][8 * j + gq][kk + 2 * tq]);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[e][8 * j + gq][kk + 2 * tq + 8]);
+                    mma_bf16_16816(acc[e][j], a0, a1, a2, a3, b0, b1);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const long long o = o_off[r0 + gq + 8 * half];
+        if (o < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int n = n0 + 8 * j + 2 * tq + i;
+                if (n >= N) continue;
+                const float v = acc[0][j][2 * half + i];
+                if (EPI == 1) {
+                    const float lin = acc[NW - 1][j][2 * half + i];
+                    ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(v / (1.f + expf(-v)) * lin);
+                } else if (p.out_f32) {
+                    ((float*)p.out)[o + n] = v;
+                } else {
+                    ((__nv_bfloat16*)p.out)[o + n] = __float2bfloat16_rn(v);
+                }
+            }
+    }
+}
+
 }  // namespace air
 
 AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_stride, const int* a_index, int a_div,
@@ -170,6 +318,13 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
     if (row_tiles <= 0) return 0;
     if (row_tiles > 65535 || groups > 65535) return AIR_ERR_BAD_ARGUMENT;
     dim3 grid((N + air::GG_BN - 1) / air::GG_BN, row_tiles, start ? 1 : groups);
+    // the tensor-core kernel fetches 8 elements at a time: every row of A and of W must start on 16 bytes
+    const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_group_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 &&
+                         ((uintptr_t)W & 15) == 0;
+    if (dtype == AIR_BF16 && aligned) {
+        if (epi == 1) return air::launch(air::grouped_gemm_tc_kernel<1>, grid, 128, 0, stream, p);
+        return air::launch(air::grouped_gemm_tc_kernel<0>, grid, 128, 0, stream, p);
+    }
     AIR_DISPATCH(dtype, TT, {
         if (epi == 1) return air::launch(air::grouped_gemm_kernel<TT, 1>, grid, 256, 0, stream, p);
         return air::launch(air::grouped_gemm_kernel<TT, 0>, grid, 256, 0, stream, p);

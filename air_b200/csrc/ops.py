@@ -38,6 +38,10 @@ _SIGNATURES = {
     "air_latent_prepare": [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p],
+    "air_gather_keys": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                        c_void_p, c_void_p],
+    "air_masked_softmax": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                           c_void_p, c_void_p],
     "air_moe_route": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
@@ -110,7 +114,7 @@ TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_m
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
                12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
                17: "qkv_prepare", 18: "glu", 19: "scaled_norm", 20: "post_norm", 21: "qk_normed_prepare",
-               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm"}
+               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -370,6 +374,42 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
         int(chunk or window or 0), float(scale), float(softcap or 0.0), 1 if chunk else 0, _ptr(sink),
         1 if latent else 0, _stream()), "paged_attention_ref")
     return out
+
+
+def gather_keys(cache, table_row, lo, count, keys, values, kv_heads=1, page_tokens=None, latent=False):
+    """The keys lo .. lo + count of the request whose block-table row is table_row, from the pages into keys
+    [G, Lp, dk] (and values [G, Lp, dv]; latent: cache [pages, P, dk], keys [1, Lp, dk], no values).  Rows count .. Lp
+    are zeroed."""
+    G, Lp, dk = keys.shape
+    _req(keys, "keys", _FLOATS)
+    _req(cache, "cache", (keys.dtype,))
+    _req(table_row, "table_row", _I32)
+    dv = 0
+    if latent:
+        P = cache.shape[1]
+    else:
+        _req(values, "values", (keys.dtype,), (G, Lp, None))
+        dv, P = values.shape[2], int(page_tokens)
+    _check(_get("air_gather_keys")(cache.data_ptr(), _DT[keys.dtype], table_row.data_ptr(), int(lo), int(count), Lp,
+                                   int(kv_heads), dk, dv, P, 1 if latent else 0, keys.data_ptr(),
+                                   None if latent else values.data_ptr(), _stream()), "gather_keys")
+
+
+def masked_softmax(scores, weights, heads_per_group, lo, count, pos0, scale, window=None, chunk=None, sink=None):
+    """scores float32 [G, n * J, Lp] -> weights bfloat16 of the same shape: the softmax of scale * scores over the keys
+    that each row's query sees (column c = key lo + c, c < count; row (t, j) = the query at pos0 + t of head g * J + j),
+    with exp(sink[h]) in the denominator where sink (float32 [G * J]) is given."""
+    G, rows, Lp = scores.shape
+    J = int(heads_per_group)
+    _req(scores, "scores", (torch.float32,))
+    _req(weights, "weights", (torch.bfloat16,), (G, rows, Lp))
+    if sink is not None:
+        _req(sink, "sink", (torch.float32,), (G * J,))
+    if window and chunk:
+        raise KernelError("masked_softmax: a window or a chunk, not both")
+    _check(_get("air_masked_softmax")(scores.data_ptr(), weights.data_ptr(), G, rows // J, J, int(count), Lp, int(lo),
+                                      int(pos0), int(chunk or window or 0), 1 if chunk else 0, float(scale), _ptr(sink),
+                                      _stream()), "masked_softmax")
 
 
 def post_norm(h, alpha, a, b, b_row_scale, weight, eps, out):

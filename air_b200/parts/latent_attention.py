@@ -7,12 +7,13 @@ from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import Mixer, PagedLatent
+from .gathered_attention import PortionAttention
 from .linear import Linear
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
 @register_mixer("latent_attention")
-class LatentAttention(Mixer):
+class LatentAttention(PortionAttention, Mixer):
     """q = Wq x, per head [head_dim plain | rot_dim rotated].  (c | kr) = Wdkv x: c (kv_rank columns) is normalised,
     c = rms(c) * w_c; kr (rot_dim columns) is one rotated key part for all heads.  Head h has the key [Wuk_h c | kr]
     and the value Wuv_h c; score = scale * (q_plain . Wuk_h c + q_rot . kr); causal softmax over the last `window` keys
@@ -37,7 +38,7 @@ class LatentAttention(Mixer):
         self.hidden, self.heads, self.head_dim = p["hidden"], p["heads"], p["head_dim"]
         self.rot_dim, self.v_dim, self.rank = p["rot_dim"], p["v_dim"], p["kv_rank"]
         self.scale, self.eps = float(p["scale"]), float(p.get("eps", 1e-6))
-        self.window, self.borrows = p.get("window"), bool(p.get("borrows", False))
+        self.window, self.borrows, self.chunk, self.sinks = p.get("window"), bool(p.get("borrows", False)), None, None
         self.keep = p.get("keep", self.window) if self.window else None
         if self.rank + self.rot_dim > 640:
             raise ConfigError("unsupported", f"latent attention: rows of {self.rank + self.rot_dim} numbers: the "
@@ -96,8 +97,7 @@ class LatentAttention(Mixer):
         ops.grouped_gemm(q_plain, self.uk_t, q_full, R, d, lda=H * d, ldo=H * (R + rot), groups=H, a_group_stride=d,
                          o_group_stride=R + rot, a_local=True, o_local=True, rows_per_group=T)
         summed = torch.empty((T, H, R), dtype=rt.dtype, device=dev)
-        ops.paged_attention_ref(q_full, latent.rows, bt, ctx.token_seq, ctx.positions, summed, self.window, self.scale,
-                                latent=True)
+        self.attend(q_full, latent.rows, bt, ctx, summed, latent=True)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=dev)
         ops.grouped_gemm(summed, self.uv, out, dv, R, lda=H * R, ldo=H * dv, groups=H, a_group_stride=R,
                          o_group_stride=dv, a_local=True, o_local=True, rows_per_group=T)

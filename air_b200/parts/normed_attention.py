@@ -7,12 +7,13 @@ from ..config.model_config import ConfigError
 from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import Mixer, PagedKV
+from .gathered_attention import PortionAttention
 from .linear import Linear
 from .registry import register_mixer, POSITION_ENCODINGS
 
 
 @register_mixer("normed_attention")
-class NormedAttention(Mixer):
+class NormedAttention(PortionAttention, Mixer):
     """Causal softmax attention over the paged cache in which
 
       * keys and queries have one size per head (head_dim) and values another (v_dim); query head h reads key/value
@@ -32,7 +33,8 @@ class NormedAttention(Mixer):
     q.norm, k.norm [head_dim] where qk_norm, sink [heads] where sink, o [hidden, heads*v_dim].
 
     q, k and v are one product; one kernel then normalises, rotates and writes keys and values to the pages; pages of a
-    chunk that no later query can see go back to the pool."""
+    chunk that no later query can see go back to the pool.  Prompt portions attend through matrix products over their
+    gathered keys, everything else through the 32-bit kernel that reads the pages (PortionAttention)."""
 
     graph_safe = True
 
@@ -104,6 +106,5 @@ class NormedAttention(Mixer):
         ops.qk_normed_prepare(proj, self.q_weight, self.k_weight, self.eps, pos.frequencies64(), pos.pairing,
                               pos.magnitude, ctx.positions, ctx.token_seq, bt, q, kv, G, dv, P, status=ctx.status)
         out = torch.empty((T, H, dv), dtype=rt.dtype, device=x.device)
-        ops.paged_attention_ref(q, kv, bt, ctx.token_seq, ctx.positions, out, self.window, self.scale, kv_heads=G,
-                                page_tokens=P, chunk=self.chunk, sink=self.sinks)
+        self.attend(q, kv, bt, ctx, out, kv_heads=G, page_tokens=P)
         return self.o.f32_sums(out.view(T, H * dv))

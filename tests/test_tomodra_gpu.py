@@ -154,6 +154,34 @@ def test_attention_sees_the_keys_inside_its_mask_and_no_other(kind, size, dtype)
             tol = 3e-4 if dtype == torch.float32 else 0.3          # (values up to 35: bfloat16 holds them to 0.125)
             assert np.abs(out.float().cpu().numpy() - want[at:at + m]).max() < tol, (at, m)
             at += m
+    if dtype != torch.bfloat16:
+        return
+    # the same rows as portions of a batch: long portions through the matrix products over gathered keys (in blocks of
+    # 100 queries here, so that blocks begin inside windows and chunks), a short one and single tokens of another
+    # request through the pages, in one step
+    from types import SimpleNamespace
+    from air_b200.parts.base import HostBatch, Runtime
+    from air_b200.parts.gathered_attention import PortionAttention
+
+    class Road(PortionAttention):
+        BLOCK = 100
+        rt = Runtime(device=torch.device(DEV), dtype=torch.bfloat16, page_tokens=P)
+        heads, kv_heads, window, chunk, sinks = H, G, size if kind == "window" else None, size if kind == "chunk" else None, dev(sink)
+
+    road = Road()
+    road.scale = scale
+    table[0, :len(pages)] = i32(pages)                  # a second request that holds the same pages
+    for counts, lengths, slots in (([1, 33, 1], [40, 0, 299], [0, 1, 0]), ([2, 261], [37, 39], [0, 1]), ([300], [0], [1])):
+        q_start = [0] + np.cumsum(counts).tolist()
+        batch = HostBatch(counts=counts, lengths=lengths, slots=slots, q_start=q_start)
+        plan = road.plan(batch)
+        positions = [p for n, l in zip(counts, lengths) for p in range(l, l + n)]
+        seq = [s_ for n, s_ in zip(counts, slots) for _ in range(n)]
+        ctx = SimpleNamespace(plans={road.plan_key(): SimpleNamespace(small_seq=i32(plan.arrays["small_seq"]), **plan.values)},
+                              token_seq=i32(seq), positions=i32(positions))
+        out = torch.empty((len(positions), H, dv), dtype=dtype, device=DEV)
+        road.attend(dev(q[positions], dtype), cache, table, ctx, out, kv_heads=G, page_tokens=P)
+        assert np.abs(out.float().cpu().numpy() - want[positions]).max() < 0.3, counts
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -349,15 +377,21 @@ def test_float32_does_not_depend_on_the_cut_or_the_batch(name):
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_bfloat16_agrees_with_itself_across_schedules(name):
-    """Rows of whole prompts against the same rows from portions and from mixed batches: rounding differs only in the
-    order of 32-bit sums, so all but a few rows (where a router's choice tips) agree far inside bfloat16's own error."""
+    """Rows of whole prompts against the same rows from portions and from mixed batches.  Long portions attend through
+    matrix products over gathered keys, short ones and single tokens through the pages, so a row's rounding depends on
+    the schedule; the rows must still agree as they agree with the oracle."""
     streams = streams_for(name, 30, (97, 40, 131))
     whole, _ = replay(name, "bfloat16", util.trace_whole(streams), page_tokens=64)
     cut, _ = replay(name, "bfloat16", util.trace_portions(streams, sizes=(2, 31, 1, 16, 5)), page_tokens=64)
     mixed, _ = replay(name, "bfloat16", util.trace_mixed(streams, seed=1, live=3), page_tokens=64, max_requests=3)
     for other in (cut, mixed):
-        far = sum(np.abs(other[key] - row).max() > 2e-2 * max(1.0, np.abs(row).max()) for key, row in whole.items())
-        assert far <= len(whole) // 20, far
+        means = []
+        for key, row in whole.items():
+            scale = max(1.0, np.abs(row).max())
+            diff = np.abs(other[key] - row)
+            assert diff.max() <= tu.BF16_MAX_TOL * scale and diff.mean() <= tu.BF16_MEAN_TOL * scale, key
+            means.append(diff.mean() / scale)
+        assert np.median(means) <= tu.BF16_MEDIAN_TOL
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
