@@ -1,0 +1,257 @@
+// Paged attention with 32-bit arithmetic in which a block serves all the query heads that share a key/value head, so
+// that a key and its value are read from memory once for the whole group: the kernel of single next tokens and short
+// portions for layers whose keys the tile kernels do not take (a latent row per token that every head reads, keys and
+// values of different sizes, chunks, a sink), in both engines, and of everything in the float32 engine.
+//
+// grouped_attention_kernel<T, JB>: block (token, key/value head and block of JB query heads of its group, split).  Keys
+//   are visited in tiles of 64 aligned to absolute positions; split s of S takes the tiles whose index is s modulo S.
+//   A tile's rows (and its values, unless the values are the keys' first columns) are staged in shared memory with
+//   16-byte loads, rows padded to an odd number of words.  Scores: a thread takes one key and JB / 4 heads, the queries
+//   wait in shared memory as float32.  Softmax: online, one warp per head in turn, 32-bit.  Weighted values: a thread
+//   takes columns tid, tid + 256, .. for all JB heads.  The block writes unnormalised sums, its maximum and its sum of
+//   weights; grouped_combine_kernel merges the splits in order, adds the sink's term to the denominator and rounds
+//   once.  What a query computes depends on its position, the split count and the cache only.
+//
+// q: [T, H, d] (float32, or the cache's type); cache: pages of keys [G, P, d] then values [G, P, dv], or (latent)
+// [P, d] whose first dv columns are the values; masks as in attention_ref.cu.  d and dv are multiples of 16 bytes.
+#include "common.cuh"
+
+namespace air {
+
+constexpr int GA_KT = 64, GA_NI = 3;      // keys per tile; columns per thread (dv up to 256 * GA_NI)
+
+template <typename T> struct Words;       // how elements lie in 32-bit words
+template <> struct Words<float> { static constexpr int per = 1; };
+template <> struct Words<__nv_bfloat16> { static constexpr int per = 2; };
+
+template <typename T, int JB>
+__global__ void __launch_bounds__(256)
+grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __restrict__ cache,
+                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
+                         const int* __restrict__ positions, float* __restrict__ part, int H, int G, int d, int dv, int P,
+                         int window, int mask_mode, float scale, int latent, int splits) {
+    constexpr int JT = JB / 4, PER = Words<T>::per;
+    extern __shared__ __align__(16) float smem[];
+    pdl_enter(TR_ATT_GROUPED);
+    const int t = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int J = H / G, hbs = (J + JB - 1) / JB;
+    const int g = blockIdx.y / hbs, j0 = (blockIdx.y % hbs) * JB, nj = min(JB, J - j0), head0 = g * J + j0;
+    const int pos = positions[t];
+    const int lo = window > 0 ? (mask_mode == 1 ? pos - pos % window : max(0, pos - window + 1)) : 0;
+    const int* bt = block_table + (size_t)slot * max_blocks;
+    const int kw = d / PER, vw = dv / PER;                 // words per row
+    const int ksw = kw | 1, vsw = vw | 1;                  // ... as staged: odd, so that rows fall into different banks
+    float* qs = smem;                                      // [JB][d]
+    float* S = qs + JB * d;                                // [JB][64]
+    float* corr = S + JB * GA_KT;                          // [JB], then the running maximum and sum
+    float* mrun = corr + JB;
+    float* lrun = mrun + JB;
+    int* pages = reinterpret_cast<int*>(lrun + JB);        // [64]: the page of each of the tile's keys
+    uint32_t* Kw = reinterpret_cast<uint32_t*>(pages + GA_KT);  // [64][ksw]
+    uint32_t* Vw = latent ? Kw : Kw + GA_KT * ksw;          // [64][vsw]
+    const int vstride = latent ? ksw : vsw;
+    for (int i = tid; i < JB * d; i += 256) {
+        const int j = i / d, e = i % d;
+        float v = 0.f;
+        if (j < nj) {
+            const size_t at = ((size_t)t * H + head0 + j) * d + e;
+            v = q_f32 ? ((const float*)q_any)[at] : to_float(((const T*)q_any)[at]);
+        }
+        qs[i] = v;
+    }
+    if (tid < JB) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }
+    float acc[JB][GA_NI];
+#pragma unroll
+    for (int j = 0; j < JB; ++j)
+#pragma unroll
+        for (int i = 0; i < GA_NI; ++i) acc[j][i] = 0.f;
+    const size_t page_stride = latent ? (size_t)P * d : (size_t)G * P * (d + dv);
+    const int kchunks = d * (int)sizeof(T) / 16, vchunks = dv * (int)sizeof(T) / 16;
+    for (int kt = lo / GA_KT + split; kt * GA_KT <= pos; kt += splits) {
+        const int key0 = kt * GA_KT;
+        __syncthreads();                                   // the tile before this one has been used
+        if (tid < GA_KT) {                                 // (looked up once, so that the loads below do not wait in turn)
+            const int key = key0 + tid;
+            pages[tid] = key >= lo && key <= pos ? bt[key / P] : -1;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int c = tid; c < GA_KT * kchunks; c += 256) {
+            const int r = c / kchunks, cc = c % kchunks, key = key0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (pages[r] >= 0) {
+                const T* row = cache + (size_t)pages[r] * page_stride +
+                               (latent ? (size_t)(key % P) * d : ((size_t)g * P + key % P) * d);
+                v = *reinterpret_cast<const uint4*>(row + cc * (16 / sizeof(T)));
+            }
+            uint32_t* dst = Kw + r * ksw + cc * 4;
+            dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+        }
+        if (!latent)
+#pragma unroll 4
+            for (int c = tid; c < GA_KT * vchunks; c += 256) {
+                const int r = c / vchunks, cc = c % vchunks, key = key0 + r;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (pages[r] >= 0) {
+                    const T* row = cache + (size_t)pages[r] * page_stride + (size_t)G * P * d +
+                                   ((size_t)g * P + key % P) * dv;
+                    v = *reinterpret_cast<const uint4*>(row + cc * (16 / sizeof(T)));
+                }
+                uint32_t* dst = Vw + r * vsw + cc * 4;
+                dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+            }
+        __syncthreads();
+        {   // scores: key kk, heads gq * JT ..
+            const int kk = tid & 63, gq = tid >> 6;
+            float s[JT];
+#pragma unroll
+            for (int jt = 0; jt < JT; ++jt) s[jt] = 0.f;
+            const uint32_t* krow = Kw + kk * ksw;
+            for (int w = 0; w < kw; ++w) {
+                const uint32_t word = krow[w];
+                if (PER == 2) {
+                    const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&word);
+                    const float k0 = __low2float(k2), k1 = __high2float(k2);
+#pragma unroll
+                    for (int jt = 0; jt < JT; ++jt) {
+                        const float2 q2 = *reinterpret_cast<const float2*>(qs + (gq * JT + jt) * d + 2 * w);
+                        s[jt] = fmaf(k1, q2.y, fmaf(k0, q2.x, s[jt]));
+                    }
+                } else {
+                    const float k0 = __uint_as_float(word);
+#pragma unroll
+                    for (int jt = 0; jt < JT; ++jt) s[jt] = fmaf(k0, qs[(gq * JT + jt) * d + w], s[jt]);
+                }
+            }
+            const int key = key0 + kk;
+            const bool seen = key >= lo && key <= pos;
+#pragma unroll
+            for (int jt = 0; jt < JT; ++jt) S[(gq * JT + jt) * GA_KT + kk] = seen ? s[jt] * scale : -INFINITY;
+        }
+        __syncthreads();
+        for (int j = warp; j < JB; j += 8) {
+            const float s0 = S[j * GA_KT + lane], s1 = S[j * GA_KT + lane + 32];
+            const float m_old = mrun[j];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+            float p0 = 0.f, p1 = 0.f, c = 1.f;
+            if (m_new != -INFINITY) {
+                p0 = expf(s0 - m_new);
+                p1 = expf(s1 - m_new);
+                c = expf(m_old - m_new);
+            }
+            const float sum = warp_sum(p0 + p1);
+            S[j * GA_KT + lane] = p0;
+            S[j * GA_KT + lane + 32] = p1;
+            if (lane == 0) { lrun[j] = lrun[j] * c + sum; mrun[j] = m_new; corr[j] = c; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < JB; ++j) {
+            const float c = corr[j];
+#pragma unroll
+            for (int i = 0; i < GA_NI; ++i) acc[j][i] *= c;
+        }
+        const T* Vt = reinterpret_cast<const T*>(Vw);
+        for (int kk = 0; kk < GA_KT; ++kk) {
+            float v[GA_NI];
+#pragma unroll
+            for (int i = 0; i < GA_NI; ++i) {
+                const int c = tid + 256 * i;
+                v[i] = c < dv ? to_float(Vt[(size_t)kk * vstride * PER + c]) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < JB; ++j) {
+                const float p = S[j * GA_KT + kk];
+#pragma unroll
+                for (int i = 0; i < GA_NI; ++i) acc[j][i] = fmaf(p, v[i], acc[j][i]);
+            }
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < JB; ++j) {
+        if (j >= nj) continue;
+        float* dst = part + (((size_t)t * H + head0 + j) * splits + split) * (dv + 2);
+#pragma unroll
+        for (int i = 0; i < GA_NI; ++i) {
+            const int c = tid + 256 * i;
+            if (c < dv) dst[c] = acc[j][i];
+        }
+        if (tid == 0) { dst[dv] = mrun[j]; dst[dv + 1] = lrun[j]; }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+grouped_combine_kernel(const float* __restrict__ part, const int* __restrict__ token_seq, const float* __restrict__ sink,
+                       T* __restrict__ out, int H, int dv, int splits) {
+    pdl_enter(TR_ATT_GROUPED);
+    const int t = blockIdx.x, h = blockIdx.y;
+    if (token_seq[t] < 0) return;
+    const float* p = part + ((size_t)t * H + h) * splits * (dv + 2);
+    float m = sink ? sink[h] : -INFINITY;
+    for (int s = 0; s < splits; ++s) m = fmaxf(m, p[s * (dv + 2) + dv]);
+    float total = sink ? expf(sink[h] - m) : 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = p[s * (dv + 2) + dv];
+        if (ms != -INFINITY) total += p[s * (dv + 2) + dv + 1] * expf(ms - m);
+    }
+    const float inv = 1.f / total;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = p[s * (dv + 2) + dv];
+            if (ms != -INFINITY) o += p[s * (dv + 2) + c] * expf(ms - m);
+        }
+        out[((size_t)t * H + h) * dv + c] = from_float<T>(o * inv);
+    }
+}
+
+template <typename T, int JB>
+int launch_grouped(const void* q, int q_f32, const void* cache, const int* block_table, int max_blocks,
+                   const int* token_seq, const int* positions, float* part, int T_, int H, int G, int d, int dv, int P,
+                   int window, int mask_mode, float scale, int latent, int splits, cudaStream_t stream) {
+    constexpr int PER = Words<T>::per;
+    const int ksw = (d / PER) | 1, vsw = (dv / PER) | 1;
+    const size_t smem = sizeof(float) * ((size_t)JB * d + JB * GA_KT + 3 * JB + GA_KT) +
+                        4 * (size_t)GA_KT * (ksw + (latent ? 0 : vsw));
+    if (smem > 227 * 1024) return AIR_ERR_BAD_ARGUMENT;
+    auto kernel = grouped_attention_kernel<T, JB>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int J = H / G;
+    dim3 grid(T_, G * ((J + JB - 1) / JB), splits);
+    return launch(kernel, grid, 256, smem, stream, q, q_f32, (const T*)cache, block_table, max_blocks, token_seq,
+                  positions, part, H, G, d, dv, P, window, mask_mode, scale, latent, splits);
+}
+
+}  // namespace air
+
+// part: float32 [T, H, splits, dv + 2] of scratch.
+AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, int dtype, const int* block_table,
+                                  int max_blocks, const int* token_seq, const int* positions, float* part, void* out,
+                                  int T, int H, int G, int d, int dv, int P, int window, float scale, int mask_mode,
+                                  const float* sink, int latent, int splits, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int bytes = dtype == AIR_F32 ? 4 : 2;
+    if (d <= 0 || dv <= 0 || dv > 256 * air::GA_NI || (d * bytes) % 16 || (dv * bytes) % 16 || H <= 0 || G <= 0 ||
+        H % G || splits <= 0 || splits > 65535 || mask_mode < 0 || mask_mode > 1 || (latent && (dv > d || G != 1)))
+        return AIR_ERR_BAD_ARGUMENT;
+    const int J = H / G;
+    int rc = 0;
+    AIR_DISPATCH(dtype, TT, {
+        if (J > 4)
+            rc = air::launch_grouped<TT, 16>(q, q_f32, cache, block_table, max_blocks, token_seq, positions, part, T, H,
+                                             G, d, dv, P, window, mask_mode, scale, latent, splits, stream);
+        else
+            rc = air::launch_grouped<TT, 4>(q, q_f32, cache, block_table, max_blocks, token_seq, positions, part, T, H,
+                                            G, d, dv, P, window, mask_mode, scale, latent, splits, stream);
+        if (rc) return rc;
+        return air::launch(air::grouped_combine_kernel<TT>, dim3(T, H), 128, 0, stream, part, token_seq, sink, (TT*)out,
+                           H, dv, splits);
+    });
+    return 0;
+}
+
+AIR_API int air_trace_set_attention_grouped(unsigned long long* buffer) { return air::set_trace_here(buffer); }

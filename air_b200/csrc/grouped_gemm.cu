@@ -12,8 +12,9 @@
 //   Where a slot's row of C goes: with o_index, p = o_index[slot]: part p % o_div, row p / o_div of out
 //   [o_div, rows, N] (o_part_stride elements per part); else row `slot` (or, o_local, the row inside the group) plus
 //   g * o_group_stride.
-//   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], rows 0 .. F the gate's and F .. 2 F the
-//   linear branch's; C [rows, F] = silu(gate) * linear in A's type.
+//   Epilogue 0: C as float32 or in A's type.  Epilogue 1: W_g is [2 F, K], blocks of gate_block rows of the gate and
+//   as many of the linear branch in turn (gate_block = F: all gate rows, then all linear rows), the arrangement that
+//   the dense gated feed-forward uses; C [rows, F] = silu(gate) * linear in A's type.
 //
 // Arithmetic.  float32 operands (and bfloat16 ones whose strides are not multiples of 8 elements): 32-bit multiply-adds
 // on the CUDA cores, k ascending; a tile is 64 x 64, a thread holds 4 x 4 of it (grouped_gemm_kernel).  bfloat16
@@ -33,6 +34,7 @@ struct GroupedArgs {
     int o_local; int out_f32;
     const int* start; int rows_per_group; const int* tiles; const int* num_tiles;
     int N, K;
+    int gate_block;      // epilogue 1: rows of W_g come in blocks of gate_block gate rows and as many linear rows in turn
 };
 
 constexpr int GG_BM = 64, GG_BN = 64, GG_BK = 16;
@@ -113,7 +115,8 @@ grouped_gemm_kernel(const GroupedArgs p) {
 #pragma unroll
             for (int e = 0; e < (EPI == 1 ? 2 : 1); ++e) {
                 const int n = n0 + lm;
-                Ws[e][lk + i][lm] = (n < N && k < K) ? to_float(W[((size_t)e * N + n) * K + k]) : 0.f;
+                const size_t wrow = EPI == 1 ? (size_t)(n / p.gate_block) * 2 * p.gate_block + e * p.gate_block + n % p.gate_block : n;
+                Ws[e][lk + i][lm] = (n < N && k < K) ? to_float(W[wrow * K + k]) : 0.f;
             }
         }
         __syncthreads();
@@ -222,7 +225,8 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
 #pragma unroll
             for (int e = 0; e < NW; ++e) {
                 const int n = n0 + row;
-                rw[e][i] = (n < N && k < K) ? ldg16(W + ((size_t)e * N + n) * K + k) : make_uint4(0, 0, 0, 0);
+                const size_t wrow = EPI == 1 ? (size_t)(n / p.gate_block) * 2 * p.gate_block + e * p.gate_block + n % p.gate_block : n;
+                rw[e][i] = (n < N && k < K) ? ldg16(W + wrow * K + k) : make_uint4(0, 0, 0, 0);
             }
         }
     };
@@ -306,14 +310,16 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
                              long long ldo, long long o_group_stride, const int* o_index, int o_div,
                              long long o_part_stride, int o_local, int out_f32, const int* start, int rows_per_group,
                              const int* tiles, const int* num_tiles, int max_tiles, int groups, int N, int K,
-                             int dtype, int epi, cudaStream_t stream) {
+                             int dtype, int epi, int gate_block, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || groups <= 0) return 0;
     if ((start != nullptr) != (tiles != nullptr) || (start && !num_tiles) || epi < 0 || epi > 1 ||
         (a_index && a_div <= 0) || (o_index && o_div <= 0) || (a_scale && !a_index))
         return AIR_ERR_BAD_ARGUMENT;
+    if (epi == 1 && gate_block <= 0) gate_block = N;
+    if (epi == 1 && N % gate_block) return AIR_ERR_BAD_ARGUMENT;
     air::GroupedArgs p{A, lda, a_group_stride, a_index, a_div, a_local, a_scale, W, w_group_stride, out, ldo,
                        o_group_stride, o_index, o_div, o_part_stride, o_local, out_f32, start, rows_per_group, tiles,
-                       num_tiles, N, K};
+                       num_tiles, N, K, gate_block};
     const int row_tiles = start ? max_tiles : (rows_per_group + air::GG_BM - 1) / air::GG_BM;
     if (row_tiles <= 0) return 0;
     if (row_tiles > 65535 || groups > 65535) return AIR_ERR_BAD_ARGUMENT;

@@ -127,7 +127,47 @@ moe_sort_kernel(const int* __restrict__ expert, int pairs, int n, int tile_rows,
     }
 }
 
+// rows_by_index_kernel: out[s, :] = x[index[s] / div, :] * scale[index[s]] (scale may be absent), in out's type: a
+// token's row once per choice, in the experts' order, with the choice's weight on it.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rows_by_index_kernel(const T* __restrict__ x, const int* __restrict__ index, int div, const float* __restrict__ scale,
+                     T* __restrict__ out, int E) {
+    pdl_enter(TR_MOE_SORT);
+    const int s = blockIdx.x, p = index[s];
+    const float m = scale ? scale[p] : 1.f;
+    const T* src = x + (size_t)(p / div) * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)s * E + i] = from_float<T>(to_float(src[i]) * m);
+}
+
+// planes_by_index_kernel: out[index[s] % div][index[s] / div][:] = rows[s][:] (float32): the experts' outputs back to
+// one plane per choice, row = token.
+__global__ void __launch_bounds__(256)
+planes_by_index_kernel(const float* __restrict__ rows, const int* __restrict__ index, int div, size_t plane,
+                       float* __restrict__ out, int E) {
+    pdl_enter(TR_MOE_SORT);
+    const int s = blockIdx.x, p = index[s];
+    float* dst = out + (size_t)(p % div) * plane + (size_t)(p / div) * E;
+    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = rows[(size_t)s * E + i];
+}
+
 }  // namespace air
+
+AIR_API int air_rows_by_index(const void* x, int dtype, const int* index, int div, const float* scale, void* out,
+                              int rows, int E, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (div <= 0) return AIR_ERR_BAD_ARGUMENT;
+    AIR_DISPATCH(dtype, TT, return air::launch(air::rows_by_index_kernel<TT>, rows, 256, 0, stream, (const TT*)x, index,
+                                               div, scale, (TT*)out, E));
+    return 0;
+}
+
+AIR_API int air_planes_by_index(const float* rows, const int* index, int div, long long plane, float* out, int n, int E,
+                                cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (div <= 0) return AIR_ERR_BAD_ARGUMENT;
+    return air::launch(air::planes_by_index_kernel, n, 256, 0, stream, rows, index, div, (size_t)plane, out, E);
+}
 
 AIR_API int air_moe_route(const float* z, int ld, int T, int n, int top, int score, int renormalize, int has_gate,
                           int* expert, float* weight, float* gate, cudaStream_t stream) {

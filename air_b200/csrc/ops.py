@@ -38,6 +38,9 @@ _SIGNATURES = {
     "air_latent_prepare": [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                            c_void_p],
+    "air_grouped_attention": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int,
+                              c_void_p],
     "air_gather_keys": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                         c_void_p, c_void_p],
     "air_masked_softmax": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -46,7 +49,9 @@ _SIGNATURES = {
     "air_moe_sort": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "air_grouped_gemm": [c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p, c_longlong,
                          c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
-                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "air_rows_by_index": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "air_planes_by_index": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
     "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
@@ -114,7 +119,7 @@ TRACE_NAMES = {1: "embedding", 2: "add_rmsnorm", 3: "qkv_rope_store", 4: "silu_m
                7: "attention_ref", 8: "decode_attention", 9: "decode_combine", 10: "prefill_attention", 11: "gemm_f32",
                12: "gemm_tc", 13: "sample", 14: "short_conv", 15: "linear_scan", 16: "gated_rmsnorm",
                17: "qkv_prepare", 18: "glu", 19: "scaled_norm", 20: "post_norm", 21: "qk_normed_prepare",
-               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax"}
+               22: "latent_prepare", 23: "moe_route", 24: "moe_sort", 25: "grouped_gemm", 26: "gather_keys", 27: "masked_softmax", 28: "grouped_attention"}
 
 
 def set_trace(buffer: Optional[torch.Tensor]) -> None:
@@ -376,6 +381,58 @@ def paged_attention_ref(q, cache, block_table, token_seq, positions, out, window
     return out
 
 
+def grouped_attention_ok(cache_dtype, d, dv) -> bool:
+    """Whether grouped_attention takes keys of d and values of dv elements: rows of whole 16-byte pieces."""
+    size = 4 if cache_dtype == torch.float32 else 2
+    return (d * size) % 16 == 0 and (dv * size) % 16 == 0 and dv <= 768
+
+
+def grouped_attention(q, cache, block_table, token_seq, positions, out, window, scale, kv_heads=1, page_tokens=None,
+                      chunk=None, sink=None, latent=False, splits=None):
+    """paged_attention_ref's arithmetic and arguments (32-bit, any batch, window or chunk, sink, latent rows), by the
+    kernel in which a block serves all query heads of a key/value head and the keys of a token are split over
+    `splits` blocks (default: enough to fill the device); needs grouped_attention_ok(cache.dtype, d, dv)."""
+    T, H, d = q.shape
+    dv = out.shape[2]
+    _req(q, "q", _FLOATS)
+    G = 1 if latent else int(kv_heads)
+    if latent:
+        _req(cache, "cache", (out.dtype,), (None, None, d))
+        P = cache.shape[1]
+    else:
+        P = int(page_tokens)
+        _req(cache, "cache", (out.dtype,))
+        if cache[0].numel() != G * P * (d + dv):
+            raise KernelError(f"grouped_attention: a page of {cache[0].numel()} elements, not {G} x {P} x ({d} + {dv})")
+    if q.dtype != out.dtype and q.dtype != torch.float32:
+        raise KernelError("grouped_attention: q is float32 or of the cache's type")
+    if not grouped_attention_ok(cache.dtype, d, dv):
+        raise KernelError(f"grouped_attention: head sizes {d} and {dv} are not whole 16-byte pieces")
+    _req(block_table, "block_table", _I32)
+    _req(token_seq, "token_seq", _I32, (T,))
+    _req(positions, "positions", _I32, (T,))
+    _req(out, "out", (cache.dtype,), (T, H, dv))
+    if sink is not None:
+        _req(sink, "sink", (torch.float32,), (H,))
+    if window and chunk:
+        raise KernelError("grouped_attention: a window or a chunk, not both")
+    J = H // G
+    if splits is None:
+        # float32: always the same number, so that a row's sums do not depend on what else is in the batch;
+        # bfloat16: as many as fill the device
+        blocks = T * G * -(-J // (16 if J > 4 else 4))
+        splits = 4 if cache.dtype == torch.float32 else max(1, min(16, 296 // max(1, blocks)))
+    part = torch.empty((T, H, splits, dv + 2), dtype=torch.float32, device=q.device)
+    _check(_get("air_grouped_attention")(
+        q.data_ptr(), 1 if q.dtype == torch.float32 else 0, cache.data_ptr(), _DT[cache.dtype], block_table.data_ptr(),
+        block_table.shape[1], token_seq.data_ptr(), positions.data_ptr(), part.data_ptr(), out.data_ptr(), T, H, G, d,
+        dv, P, int(chunk or window or 0), float(scale), 1 if chunk else 0, _ptr(sink), 1 if latent else 0, int(splits),
+        _stream()), "grouped_attention")
+    global launches
+    launches += 1
+    return out
+
+
 def gather_keys(cache, table_row, lo, count, keys, values, kv_heads=1, page_tokens=None, latent=False):
     """The keys lo .. lo + count of the request whose block-table row is table_row, from the pages into keys
     [G, Lp, dk] (and values [G, Lp, dv]; latent: cache [pages, P, dk], keys [1, Lp, dk], no values).  Rows count .. Lp
@@ -537,9 +594,10 @@ def moe_sort(expert, experts, start, pair_of_slot, tiles, num_tiles):
 
 def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group_stride=0, a_index=None, a_div=1,
                  a_scale=None, a_local=False, o_index=None, o_div=1, o_part_stride=0, o_local=False, start=None,
-                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False):
+                 rows_per_group=0, tiles=None, num_tiles=None, silu_mul=False, gate_block=0):
     """out rows = a rows @ w[g]^T for every group g (w [groups, n (2n with silu_mul), k]); see grouped_gemm.cu for how
-    rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear."""
+    rows are found.  Strides in elements.  out is float32 or of a's type; with silu_mul out = silu(gate) * linear, the
+    rows of w[g] being blocks of gate_block gate rows and as many linear rows in turn (0: all gate rows first)."""
     _req(a, "a", _FLOATS)
     _req(w, "w", (a.dtype,), (groups, 2 * n if silu_mul else n, k))
     _req(out, "out", (torch.float32, a.dtype))
@@ -556,7 +614,30 @@ def grouped_gemm(a, w, out, n, k, *, lda, ldo, groups, a_group_stride=0, o_group
         w.data_ptr(), w.shape[1] * w.shape[2], out.data_ptr(), int(ldo), int(o_group_stride), _ptr(o_index), int(o_div),
         int(o_part_stride), 1 if o_local else 0, 1 if out.dtype == torch.float32 else 0, _ptr(start),
         int(rows_per_group), _ptr(tiles), _ptr(num_tiles), tiles.shape[0] if tiles is not None else 0, int(groups),
-        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, _stream()), "grouped_gemm")
+        int(n), int(k), _DT[a.dtype], 1 if silu_mul else 0, int(gate_block), _stream()), "grouped_gemm")
+    return out
+
+
+def rows_by_index(x, index, div, scale, out):
+    """out[s] = x[index[s] // div] * scale[index[s]] (scale float32 or None), in x's type."""
+    _req(x, "x", _FLOATS)
+    _req(index, "index", _I32, (out.shape[0],))
+    _req(out, "out", (x.dtype,), (None, x.shape[1]))
+    if scale is not None:
+        _req(scale, "scale", (torch.float32,))
+    _check(_get("air_rows_by_index")(x.data_ptr(), _DT[x.dtype], index.data_ptr(), int(div), _ptr(scale), out.data_ptr(),
+                                     out.shape[0], x.shape[1], _stream()), "rows_by_index")
+    return out
+
+
+def planes_by_index(rows, index, div, out):
+    """out[index[s] % div, index[s] // div] = rows[s]; rows float32 [n, E], out float32 [div, T, E]."""
+    n, E = rows.shape
+    _req(rows, "rows", (torch.float32,))
+    _req(index, "index", _I32, (n,))
+    _req(out, "out", (torch.float32,), (div, None, E))
+    _check(_get("air_planes_by_index")(rows.data_ptr(), index.data_ptr(), int(div), out.shape[1] * E, out.data_ptr(), n,
+                                       E, _stream()), "planes_by_index")
     return out
 
 

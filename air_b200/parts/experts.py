@@ -8,7 +8,7 @@ from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward, GatedSum
 from .linear import Linear
-from .mlp import SwiGLU
+from .mlp import SwiGLU, fused_gate_up_pays
 from .registry import register_feed_forward
 from .spec import PartSpec
 
@@ -37,7 +37,12 @@ class RoutedExperts(FeedForward):
     Everything happens on the device: a kernel picks the experts, one orders the (token, choice) pairs by expert, and
     two grouped products (gate and up with the activation; down) walk the experts' rows.  The outputs of a token's
     choices land in `top` planes that the norm behind the layer adds in order, so the sum does not depend on the
-    batch."""
+    batch.  A step of many tokens that is not a decode step (so never part of a CUDA graph) instead reads the experts'
+    row counts on the host, once per layer, and runs every expert's rows through the dense feed-forward's products
+    (the tcgen05 kernel with the activation in its epilogue, the library's product for down): see HOST_ROWS."""
+
+    # From so many rows per expert (in the mean) on, a bfloat16 step that holds prompt portions takes the road over the host.
+    HOST_ROWS = 64
 
     graph_safe = True
 
@@ -72,20 +77,39 @@ class RoutedExperts(FeedForward):
         super().load(tensors, rt)
         p, n = self.prefix, self.experts
         rows = [tensors[p + "router"]] + ([tensors[p + "shared.sg"]] if self.shared_gate else [])
-        # the router and the shared expert's gate are one 32-bit product on the CUDA cores
-        self.router = Linear(torch.cat([r.to(torch.float32) for r in rows], dim=0).contiguous(), rt.status)
-        self.gate_up = torch.stack([torch.cat([tensors[f"{p}e{i}.gate"], tensors[f"{p}e{i}.up"]], dim=0)
+        # The router and the shared expert's gate are one product with 32-bit sums.  In a bfloat16 engine its operands
+        # are the stored 16-bit weights and the stream's rows as the other products read them: their products are
+        # exact in 32 bits, so the tensor cores' 32-bit accumulation is the 32-bit router (rows of zeros fill the matrix
+        # up to a multiple of 8, which those kernels want).  A float32 engine runs the CUDA-core product.
+        w = torch.cat([r.to(rt.dtype) for r in rows], dim=0)
+        if not rt.is_fp32 and w.shape[0] % 8:
+            w = torch.cat([w, torch.zeros((8 - w.shape[0] % 8, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
+        self.router = Linear(w.contiguous(), rt.status)
+        # gate and up of an expert are one matrix, in the dense feed-forward's arrangement (blocks of gate rows and of up
+        # rows in turn), so that the same memory serves the grouped product and the dense products per expert
+        F = self.inter
+        block = next((b for b in (128, 64, 32) if F % b == 0), F) if rt.dtype == torch.bfloat16 else F
+        self.block = block
+
+        def arranged(g, u):
+            if block == F:
+                return torch.cat([g, u], dim=0)
+            return torch.stack([g.view(F // block, block, -1), u.view(F // block, block, -1)], dim=1).reshape(2 * F, -1)
+
+        self.gate_up = torch.stack([arranged(tensors[f"{p}e{i}.gate"], tensors[f"{p}e{i}.up"])
                                     for i in range(n)]).contiguous()             # [n, 2F, E]
         self.down = torch.stack([tensors[f"{p}e{i}.down"] for i in range(n)]).contiguous()      # [n, E, F]
         if self.gate_up.dtype != rt.dtype:
             raise ValueError(f"{p}: the experts are stored as {self.gate_up.dtype}, the engine computes in {rt.dtype}")
+        self.gate_up_of = [Linear(self.gate_up[i], rt.status, gate_up_block=block if block != F else 0) for i in range(n)]
+        self.down_of = [Linear(self.down[i], rt.status) for i in range(n)]
         if self.shared is not None:
             self.shared.load(tensors, rt)
 
     def forward(self, x, ctx):
         T, E, F, n, top = x.shape[0], self.hidden, self.inter, self.experts, self.top
         dev = x.device
-        z = self.router(x, torch.float32)
+        z = self.router.f32(x)
         expert = torch.empty((T, top), dtype=torch.int32, device=dev)
         weight = torch.empty((T, top), dtype=torch.float32, device=dev)
         gate = torch.empty((T,), dtype=torch.float32, device=dev) if self.shared_gate else None
@@ -96,12 +120,41 @@ class RoutedExperts(FeedForward):
         start, pair_of_slot = ints[:n + 1], ints[n + 1:n + 1 + pairs]
         tiles, num_tiles = ints[n + 1 + pairs:-1].view(-1, 2), ints[-1:]
         ops.moe_sort(expert, n, start, pair_of_slot, tiles, num_tiles)
-        act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
-        ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
-                         a_scale=weight.view(-1), start=start, tiles=tiles, num_tiles=num_tiles, silu_mul=True)
         y = torch.empty((top, T, E), dtype=torch.float32, device=dev)
-        ops.grouped_gemm(act, self.down, y, E, F, lda=F, ldo=E, groups=n, o_index=pair_of_slot, o_div=top,
-                         o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles)
+        if x.dtype == torch.bfloat16 and not ctx.all_decode and pairs >= self.HOST_ROWS * n:
+            self._experts_one_by_one(x, start, pair_of_slot, weight, y)
+        else:
+            act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
+            ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
+                             a_scale=weight.view(-1), start=start, tiles=tiles, num_tiles=num_tiles, silu_mul=True,
+                             gate_block=self.block)
+            ops.grouped_gemm(act, self.down, y, E, F, lda=F, ldo=E, groups=n, o_index=pair_of_slot, o_div=top,
+                             o_part_stride=T * E, start=start, tiles=tiles, num_tiles=num_tiles)
         if self.shared is None:
             return y
         return GatedSum(y, self.shared.forward(x, ctx), gate)
+
+    def _experts_one_by_one(self, x, start, pair_of_slot, weight, y):
+        """The road over the host: the rows in the experts' order with their weights on them, every expert's rows through
+        the products of the dense gated feed-forward, the results back to the planes."""
+        top, (T, E) = self.top, x.shape
+        pairs = T * top
+        rows = ops.rows_by_index(x, pair_of_slot, top, weight.view(-1), torch.empty((pairs, E), dtype=x.dtype, device=x.device))
+        outs = torch.empty((pairs, E), dtype=torch.float32, device=x.device)
+        bounds = start.tolist()              # the one read of the device per layer
+        for e in range(self.experts):
+            lo, hi = bounds[e], bounds[e + 1]
+            if hi == lo:
+                continue
+            mine, gate_up, down = rows[lo:hi], self.gate_up_of[e], self.down_of[e]
+            if gate_up.gate_up_block and (gate_up.small(mine) or fused_gate_up_pays(hi - lo, gate_up.out_features)):
+                act = gate_up.silu_mul(mine)
+            else:
+                act = torch.empty((hi - lo, self.inter), dtype=x.dtype, device=x.device)
+                ops.silu_mul(gate_up(mine, x.dtype), act, block=self.block)
+            if down.small(act):
+                outs[lo:hi].zero_()
+                ops.add_parts(outs[lo:hi], down.partial(act))
+            else:
+                torch.mm(act, down.weight.t(), out_dtype=torch.float32, out=outs[lo:hi])
+        ops.planes_by_index(outs, pair_of_slot, top, y)

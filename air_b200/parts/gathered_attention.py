@@ -17,7 +17,9 @@ class PortionAttention:
     into a dense block; scores = Q K^T is one library product per key/value head with all of the head's query heads
     as rows (32-bit out), the package's kernel takes the masked softmax (window or chunks, a sink) in 32-bit, and
     weights times values is the second product.  The rows of all other entries (single next tokens, short portions)
-    and everything in a float32 engine go through the 32-bit attention kernel, which reads the pages itself.
+    and everything in a float32 engine go through a 32-bit attention kernel that reads the pages itself: the one in
+    which a block serves all query heads of a key/value head (ops.grouped_attention), or, for sizes that are not whole
+    16-byte pieces, the one with a block per head.
 
     The mixer offers: rt, heads, kv_heads (1 for a latent), scale, window, chunk, and sinks (float32 [heads] or None)."""
 
@@ -56,9 +58,11 @@ class PortionAttention:
         plan = ctx.plans.get((self.PLAN,)) if not self.rt.is_fp32 else None
 
         def through_the_pages(token_seq):
-            ops.paged_attention_ref(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale,
-                                    kv_heads=kv_heads, page_tokens=page_tokens, chunk=self.chunk, sink=sinks,
-                                    latent=latent)
+            # (the kernel that reads a key once for all heads of its group wants rows of whole 16-byte pieces)
+            kernel = ops.grouped_attention if ops.grouped_attention_ok(cache.dtype, q.shape[2], out.shape[2]) \
+                else ops.paged_attention_ref
+            kernel(q, cache, bt, token_seq, ctx.positions, out, self.window, self.scale, kv_heads=kv_heads,
+                   page_tokens=page_tokens, chunk=self.chunk, sink=sinks, latent=latent)
 
         if plan is None or not plan.portions:
             through_the_pages(ctx.token_seq)
@@ -84,11 +88,16 @@ class PortionAttention:
                     rows = rows.view(1, nb * H, dk)
                 else:      # rows of one key/value head together: (token, query head of the group)
                     rows = rows.view(nb, G, J, dk).permute(1, 0, 2, 3).reshape(G, nb * J, dk)
-                scores = torch.bmm(rows, keys.transpose(1, 2), out_dtype=torch.float32)
+                # (one library product per key/value head: the batched call with a 32-bit result is far slower)
+                scores = torch.empty((G, nb * J, Lp), dtype=torch.float32, device=dev)
+                for g in range(G):
+                    torch.mm(rows[g], keys[g].t(), out_dtype=torch.float32, out=scores[g])
                 weights = torch.empty(scores.shape, dtype=torch.bfloat16, device=dev)
                 ops.masked_softmax(scores, weights, J, lo, L, p0, self.scale, window=self.window, chunk=self.chunk,
                                    sink=sinks)
-                summed = torch.bmm(weights, keys[:, :, :dv] if latent else values)      # [G, nb * J, dv]
+                summed = torch.empty((G, nb * J, dv), dtype=torch.bfloat16, device=dev)
+                for g in range(G):
+                    torch.mm(weights[g], keys[g, :, :dv] if latent else values[g], out=summed[g])
                 dst = out[r0 + b0:r0 + b0 + nb]
                 if G == 1:
                     dst.copy_(summed.view(nb, H, dv))

@@ -144,6 +144,8 @@ def randomize_cache(engine, torch):
     for run in range(len(engine.model.spec.order)):
         for view in engine.cache.views(run):
             kv = getattr(view, "kv", None)
+            if kv is None:
+                kv = getattr(view, "rows", None)
             if kv is not None and kv.data_ptr() not in seen:
                 seen.add(kv.data_ptr())
                 kv.normal_(0.0, 0.5, generator=g)
@@ -474,6 +476,26 @@ def _bivizen(width, layers, heads, kv_heads, ff, vocab=32000):
             "layers": [dict(order[i % 4], mlp=mlp) for i in range(layers)]}
 
 
+# Tomodra beside the Qwen2 decoder (`--design tomodra`): a latent-attention layer, one that reads its latent, and a
+# layer of chunked attention with a sink, in turn; a latent of 512 + 64 per token, heads of 128 + 64 (values 128); 16
+# experts of ff / 4 of which a token takes 2, and a shared expert of ff / 2, so that a token's feed-forward is as wide
+# as the dense one beside it.
+def _tomodra(width, layers, heads, kv_heads, ff, vocab=32000):
+    def latent(i):
+        m = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+             "mask": {"size": 1024}, "rot": {"dims": 64, "base": 5e5}}
+        if i % 3 == 1:
+            m["kv_from"] = i - 1
+        return {"type": "latent_attention", "mixer": m}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128,
+                                          "scale": 128 ** -0.5, "mask": {"size": 1024},
+                                          "rot": {"dims": 64, "base": 1e4, "scaling": {"factor": 8.0, "original": 4096,
+                                                                                      "fast": 32.0, "slow": 1.0}}}}
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2}, "shared": {"ff": ff // 2}}
+    return {"architecture": "Tomodra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": 3.0,
+            "layers": [dict(att if i % 3 == 2 else latent(i), mlp=mlp) for i in range(layers)]}
+
+
 def _qwen(width, layers, heads, kv_heads, ff, vocab=32000):
     return dict(_QWEN, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, intermediate_size=ff, rms_norm_eps=1e-5, max_window_layers=layers,
@@ -648,21 +670,25 @@ def design_kernels(width, heads, kv_heads, ff, T, batch, context):
 def design_bench(args):
     import torch
     from air_b200.engine.batch import Entry, LAST_SAMPLED
-    if args.design != "bivizen":
-        print(json.dumps({"error": f"--design {args.design}: bivizen is the design that is compared"}))
+    designs = {"bivizen": ("Bivizen", _bivizen), "tomodra": ("Tomodra", _tomodra)}
+    if args.design not in designs:
+        print(json.dumps({"error": f"--design {args.design}: the designs that are compared are {', '.join(designs)}"}))
         return 2
-    record = {"design": "Bivizen", "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    title, make = designs[args.design]
+    record = {"design": title, "beside": "Qwen2ForCausalLM", "dtype": "bf16", "data": "synthetic", "sizes": {}}
     context = args.context or 2048
     for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
         width, layers, heads, kv_heads, ff = DESIGN_SIZES[name]
         if args.layers:
             layers = args.layers
         size = {"width": width, "layers": layers, "heads": heads, "kv_heads": kv_heads, "ff": ff}
-        for label, cfg in (("bivizen", _bivizen(width, layers, heads, kv_heads, ff)), ("qwen2", _qwen(width, layers, heads, kv_heads, ff))):
+        for label, cfg in ((args.design, make(width, layers, heads, kv_heads, ff)), ("qwen2", _qwen(width, layers, heads, kv_heads, ff))):
             print(f"--- {label} at width {width}, {layers} layers", flush=True)
             size[label] = design_model(cfg, args, torch, Entry, LAST_SAMPLED)
-        if not args.skip_kernels:
+        if not args.skip_kernels and args.design == "bivizen":
             size["kernels"] = design_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
+        if not args.skip_kernels and args.design == "tomodra":
+            size["kernels"] = tomodra_kernels(width, heads, kv_heads, ff, args.prefill_tokens, args.batch, context)
         record["sizes"][name] = size
     text = json.dumps(record)
     print(text)
@@ -742,7 +768,7 @@ def main():
     ap.add_argument("--skip-decode", action="store_true", help="for profiling the prefill step alone")
     ap.add_argument("--no-graphs", action="store_true", help="launch the decode step's kernels one by one (for ncu)")
     ap.add_argument("--kernel", default="", help="prefill_attention, or prompt_elementwise (at --prefill-tokens rows): time those kernels alone and exit")
-    ap.add_argument("--design", default="", help="bivizen: prefill and decode of that design beside the Qwen2 decoder at "
+    ap.add_argument("--design", default="", help="bivizen or tomodra: prefill and decode of that design beside the Qwen2 decoder at "
                     "equal sizes, and its kernels alone beside the like kernels (another line of output; the default "
                     "workload is not run)")
     ap.add_argument("--design-sizes", default="", help="with --design: which of the sizes 2048,4096 (default: both)")

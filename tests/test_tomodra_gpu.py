@@ -147,12 +147,14 @@ def test_attention_sees_the_keys_inside_its_mask_and_no_other(kind, size, dtype)
     for cuts in ([2, 61, T - 63], [T - 3, 1, 1, 1]):
         at = 0
         for m in cuts:
-            out = torch.empty((m, H, dv), dtype=dtype, device=DEV)
-            ops.paged_attention_ref(dev(q[at:at + m], dtype), cache, table, i32([1] * m), i32(range(at, at + m)), out,
-                                    size if kind == "window" else None, scale, kv_heads=G, page_tokens=P,
-                                    chunk=size if kind == "chunk" else None, sink=dev(sink))
-            tol = 3e-4 if dtype == torch.float32 else 0.3          # (values up to 35: bfloat16 holds them to 0.125)
-            assert np.abs(out.float().cpu().numpy() - want[at:at + m]).max() < tol, (at, m)
+            for kernel, more in ((ops.paged_attention_ref, {}), (ops.grouped_attention, {}),
+                                 (ops.grouped_attention, {"splits": 3})):
+                out = torch.empty((m, H, dv), dtype=dtype, device=DEV)
+                kernel(dev(q[at:at + m], dtype), cache, table, i32([1] * m), i32(range(at, at + m)), out,
+                       size if kind == "window" else None, scale, kv_heads=G, page_tokens=P,
+                       chunk=size if kind == "chunk" else None, sink=dev(sink), **more)
+                tol = 3e-4 if dtype == torch.float32 else 0.3          # (values up to 35: bfloat16 holds them to 0.125)
+                assert np.abs(out.float().cpu().numpy() - want[at:at + m]).max() < tol, (at, m, kernel.__name__)
             at += m
     if dtype != torch.bfloat16:
         return
@@ -185,7 +187,7 @@ def test_attention_sees_the_keys_inside_its_mask_and_no_other(kind, size, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,rot,R,dv,window", [(4, 24, 8, 40, 20, 48), (1, 32, 16, 56, 40, None), (3, 8, 4, 300, 8, 17)])
+@pytest.mark.parametrize("H,d,rot,R,dv,window", [(4, 24, 8, 40, 20, 48), (1, 32, 16, 56, 40, None), (3, 8, 4, 300, 8, 17), (16, 32, 16, 112, 24, 40), (7, 16, 8, 600, 8, None)])
 def test_latent_attention_through_its_kernels(H, d, rot, R, dv, window, dtype):
     """From the projection's output to the heads' outputs: the rows in the pages, the queries carried through the key
     expansion, attention over the rows, the value expansion.  Against keys and values expanded per head, as the
@@ -232,6 +234,10 @@ def test_latent_attention_through_its_kernels(H, d, rot, R, dv, window, dtype):
                          o_group_stride=R + rot, a_local=True, o_local=True, rows_per_group=cut)
         summed = torch.empty((cut, H, R), dtype=dtype, device=DEV)
         ops.paged_attention_ref(q_full, rows, table, seq, pos, summed, window, scale, latent=True)
+        if ops.grouped_attention_ok(dtype, R + rot, R):
+            again = torch.empty((cut, H, R), dtype=dtype, device=DEV)
+            ops.grouped_attention(q_full, rows, table, seq, pos, again, window, scale, latent=True)
+            assert np.abs(again.float().cpu().numpy() - summed.float().cpu().numpy()).max() < (1e-5 if dtype == torch.float32 else 2e-2)
         out = torch.empty((cut, H, dv), dtype=dtype, device=DEV)
         ops.grouped_gemm(summed, uv_d, out, dv, R, lda=H * R, ldo=H * dv, groups=H, a_group_stride=R,
                          o_group_stride=dv, a_local=True, o_local=True, rows_per_group=cut)
@@ -364,6 +370,20 @@ def test_unequal_requests_together_with_pages_and_slots_used_again(name, dtype, 
         assert group.pool.takes > group.pool.num_pages, "pages were used again"
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_experts_one_by_one_over_the_host(name, monkeypatch):
+    """The road that steps of many tokens take through the experts (row counts read on the host, every expert's rows
+    through the dense feed-forward's products), forced for short prompts too; experts that nobody chose, experts with
+    one row, mixed batches."""
+    from air_b200.parts.experts import RoutedExperts
+    monkeypatch.setattr(RoutedExperts, "HOST_ROWS", 1)
+    streams = streams_for(name, 70, (3, 150, 41))
+    got, _ = replay(name, "bfloat16", util.trace_whole(streams), page_tokens=64)
+    tu.check(got, name, streams, "bfloat16")
+    got, _ = replay(name, "bfloat16", util.trace_mixed(streams, seed=4, live=3), page_tokens=64, max_requests=3)
+    tu.check(got, name, streams, "bfloat16")
+
+
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_float32_does_not_depend_on_the_cut_or_the_batch(name):
     streams = streams_for(name, 30, (97, 40, 131))
@@ -389,7 +409,8 @@ def test_bfloat16_agrees_with_itself_across_schedules(name):
         for key, row in whole.items():
             scale = max(1.0, np.abs(row).max())
             diff = np.abs(other[key] - row)
-            assert diff.max() <= tu.BF16_MAX_TOL * scale and diff.mean() <= tu.BF16_MEAN_TOL * scale, key
+            # (each is within the row limits of the oracle: together twice that)
+            assert diff.max() <= 2 * tu.BF16_MAX_TOL * scale and diff.mean() <= 2 * tu.BF16_MEAN_TOL * scale, key
             means.append(diff.mean() / scale)
         assert np.median(means) <= tu.BF16_MEDIAN_TOL
 
