@@ -19,7 +19,7 @@
 // Arithmetic.  float32 operands (and bfloat16 ones whose strides are not multiples of 8 elements): 32-bit multiply-adds
 // on the CUDA cores, k ascending; a tile is 64 x 64, a thread holds 4 x 4 of it (grouped_gemm_kernel).  bfloat16
 // operands: the warp-level tensor-core instruction (m16n8k16, 32-bit accumulators), four warps of 16 rows by 64
-// columns each, operands staged through shared memory in steps of 32 of k with the next step's loads in flight
+// columns each, operands brought into a ring of four shared-memory stages by cp.async in steps of 32 of k
 // (grouped_gemm_tc_kernel).  Either way a row's result depends on nothing but the row and W_g.
 #include "common.cuh"
 #include "mma.cuh"
@@ -160,13 +160,28 @@ grouped_gemm_kernel(const GroupedArgs p) {
 
 // ---------------------------------------------------------------------------------------------- bfloat16, tensor cores
 constexpr int GT_BK = 32, GT_LD = GT_BK + 8;      // a row of a staged tile: 32 elements and 16 bytes of padding
+constexpr int GT_STAGES = 4;                      // steps of k in flight: a step of few rows is a stream of weights
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;             // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t scaled_pair(uint32_t word, float m) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&word);
+    return pack_bf16(__low2float(x) * m, __high2float(x) * m);
+}
 
 template <int EPI>
 __global__ void __launch_bounds__(128)
 grouped_gemm_tc_kernel(const GroupedArgs p) {
     constexpr int NW = EPI == 1 ? 2 : 1;
-    __shared__ __align__(16) __nv_bfloat16 As[GG_BM][GT_LD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[NW][GG_BN][GT_LD];
+    constexpr int TILE = GG_BM * GT_LD;           // elements of one staged tile
+    extern __shared__ __align__(16) __nv_bfloat16 staged[];      // [stages][1 + NW][64][GT_LD]
     __shared__ long long a_off[GG_BM], o_off[GG_BM];
     __shared__ float a_mul[GG_BM];
     pdl_enter(TR_GROUPED_GEMM);
@@ -214,43 +229,37 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
     const __nv_bfloat16* W = (const __nv_bfloat16*)p.W + (size_t)g * p.w_group_stride;
     const int N = p.N, K = p.K;
     const bool scaled = p.a_scale != nullptr;
-    // what this thread stages per step: chunks (16 bytes, 8 of k) c = tid and tid + 128 of the 64 x 4 chunks of a tile
-    uint4 ra[2], rw[NW][2];
-    auto fetch = [&](int k0) {
+    // what this thread brings per step: chunks (16 bytes, 8 of k) tid and tid + 128 of the 64 x 4 chunks of every tile
+    const __nv_bfloat16* src_a[2];
+    const __nv_bfloat16* src_w[NW][2];
+    int dst_at[2], kc_of[2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int c = tid + 128 * i, row = c >> 2, k = k0 + (c & 3) * 8;
-            const long long arow = a_off[row];
-            ra[i] = (arow >= 0 && k < K) ? ldg16(A + arow + k) : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < 2; ++i) {
+        const int c = tid + 128 * i, row = c >> 2;
+        kc_of[i] = (c & 3) * 8;
+        dst_at[i] = row * GT_LD + kc_of[i];
+        src_a[i] = a_off[row] >= 0 ? A + a_off[row] + kc_of[i] : nullptr;
 #pragma unroll
-            for (int e = 0; e < NW; ++e) {
-                const int n = n0 + row;
-                const size_t wrow = EPI == 1 ? (size_t)(n / p.gate_block) * 2 * p.gate_block + e * p.gate_block + n % p.gate_block : n;
-                rw[e][i] = (n < N && k < K) ? ldg16(W + wrow * K + k) : make_uint4(0, 0, 0, 0);
-            }
+        for (int e = 0; e < NW; ++e) {
+            const int n = n0 + row;
+            const size_t wrow = EPI == 1 ? (size_t)(n / p.gate_block) * 2 * p.gate_block + e * p.gate_block + n % p.gate_block : n;
+            src_w[e][i] = n < N ? W + wrow * K + kc_of[i] : nullptr;
         }
-    };
-    auto stage = [&]() {
+    }
+    auto bring = [&](int stage, int k0) {
+        __nv_bfloat16* base = staged + (size_t)stage * (1 + NW) * TILE;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int c = tid + 128 * i, row = c >> 2, kc = (c & 3) * 8;
-            uint4 v = ra[i];
-            if (scaled) {
-                const float m = a_mul[row];
-                uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
+            const bool in_k = k0 + kc_of[i] < K;
+            cp_async16(base + dst_at[i], src_a[i] ? src_a[i] + k0 : (const __nv_bfloat16*)A, in_k && src_a[i]);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&w32[j]);
-                    w32[j] = pack_bf16(__low2float(x) * m, __high2float(x) * m);
-                }
-            }
-            *reinterpret_cast<uint4*>(&As[row][kc]) = v;
-#pragma unroll
-            for (int e = 0; e < NW; ++e) *reinterpret_cast<uint4*>(&Ws[e][row][kc]) = rw[e][i];
+            for (int e = 0; e < NW; ++e)
+                cp_async16(base + (1 + e) * TILE + dst_at[i], src_w[e][i] ? src_w[e][i] + k0 : W, in_k && src_w[e][i]);
         }
     };
     const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
     const int r0 = warp * 16;
+    const float m_lo = a_mul[r0 + gq], m_hi = a_mul[r0 + gq + 8];
     float acc[NW][8][4];
 #pragma unroll
     for (int e = 0; e < NW; ++e)
@@ -258,28 +267,41 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
         for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[e][j][i] = 0.f;
-    fetch(0);
-    for (int k0 = 0; k0 < K; k0 += GT_BK) {
-        stage();
-        __syncthreads();
-        if (k0 + GT_BK < K) fetch(k0 + GT_BK);
+    const int steps = (K + GT_BK - 1) / GT_BK;
+#pragma unroll
+    for (int s = 0; s < GT_STAGES - 1; ++s) {
+        if (s < steps) bring(s, s * GT_BK);
+        cp_async_commit();
+    }
+    for (int step = 0; step < steps; ++step) {
+        cp_async_wait<GT_STAGES - 2>();           // this step's tiles have landed (for this thread's copies)
+        __syncthreads();                          // ... for everybody's, and the stage refilled below has been read
+        if (step + GT_STAGES - 1 < steps) bring((step + GT_STAGES - 1) % GT_STAGES, (step + GT_STAGES - 1) * GT_BK);
+        cp_async_commit();
+        const __nv_bfloat16* As = staged + (size_t)(step % GT_STAGES) * (1 + NW) * TILE;
 #pragma unroll
         for (int kk = 0; kk < GT_BK; kk += 16) {
-            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq][kk + 2 * tq]);
-            const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq + 8][kk + 2 * tq]);
-            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq][kk + 2 * tq + 8]);
-            const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&As[r0 + gq + 8][kk + 2 * tq + 8]);
+            uint32_t a0 = *reinterpret_cast<const uint32_t*>(As + (r0 + gq) * GT_LD + kk + 2 * tq);
+            uint32_t a1 = *reinterpret_cast<const uint32_t*>(As + (r0 + gq + 8) * GT_LD + kk + 2 * tq);
+            uint32_t a2 = *reinterpret_cast<const uint32_t*>(As + (r0 + gq) * GT_LD + kk + 2 * tq + 8);
+            uint32_t a3 = *reinterpret_cast<const uint32_t*>(As + (r0 + gq + 8) * GT_LD + kk + 2 * tq + 8);
+            if (scaled) {      // the weight of the row's choice, rounded as a scaled copy of the row would be
+                a0 = scaled_pair(a0, m_lo); a2 = scaled_pair(a2, m_lo);
+                a1 = scaled_pair(a1, m_hi); a3 = scaled_pair(a3, m_hi);
+            }
 #pragma unroll
-            for (int e = 0; e < NW; ++e)
+            for (int e = 0; e < NW; ++e) {
+                const __nv_bfloat16* Ws = As + (1 + e) * TILE;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[e][8 * j + gq][kk + 2 * tq]);
-                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[e][8 * j + gq][kk + 2 * tq + 8]);
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t*>(Ws + (8 * j + gq) * GT_LD + kk + 2 * tq);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t*>(Ws + (8 * j + gq) * GT_LD + kk + 2 * tq + 8);
                     mma_bf16_16816(acc[e][j], a0, a1, a2, a3, b0, b1);
                 }
+            }
         }
-        __syncthreads();
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const long long o = o_off[r0 + gq + 8 * half];
@@ -328,8 +350,12 @@ AIR_API int air_grouped_gemm(const void* A, long long lda, long long a_group_str
     const bool aligned = K % 8 == 0 && lda % 8 == 0 && a_group_stride % 8 == 0 && ((uintptr_t)A & 15) == 0 &&
                          ((uintptr_t)W & 15) == 0;
     if (dtype == AIR_BF16 && aligned) {
-        if (epi == 1) return air::launch(air::grouped_gemm_tc_kernel<1>, grid, 128, 0, stream, p);
-        return air::launch(air::grouped_gemm_tc_kernel<0>, grid, 128, 0, stream, p);
+        const size_t smem = (size_t)air::GT_STAGES * (epi == 1 ? 3 : 2) * air::GG_BM * air::GT_LD * 2;
+        if (epi == 1) {
+            cudaFuncSetAttribute(air::grouped_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            return air::launch(air::grouped_gemm_tc_kernel<1>, grid, 128, smem, stream, p);
+        }
+        return air::launch(air::grouped_gemm_tc_kernel<0>, grid, 128, smem, stream, p);
     }
     AIR_DISPATCH(dtype, TT, {
         if (epi == 1) return air::launch(air::grouped_gemm_kernel<TT, 1>, grid, 256, 0, stream, p);

@@ -140,15 +140,16 @@ rows_by_index_kernel(const T* __restrict__ x, const int* __restrict__ index, int
     for (int i = threadIdx.x; i < E; i += blockDim.x) out[(size_t)s * E + i] = from_float<T>(to_float(src[i]) * m);
 }
 
-// planes_by_index_kernel: out[index[s] % div][index[s] / div][:] = rows[s][:] (float32): the experts' outputs back to
-// one plane per choice, row = token.
+// planes_by_index_kernel: out[index[s] % div][index[s] / div][:] = rows[s][:] (out float32): the experts' outputs back
+// to one plane per choice, row = token.
+template <typename T>
 __global__ void __launch_bounds__(256)
-planes_by_index_kernel(const float* __restrict__ rows, const int* __restrict__ index, int div, size_t plane,
+planes_by_index_kernel(const T* __restrict__ rows, const int* __restrict__ index, int div, size_t plane,
                        float* __restrict__ out, int E) {
     pdl_enter(TR_MOE_SORT);
     const int s = blockIdx.x, p = index[s];
     float* dst = out + (size_t)(p % div) * plane + (size_t)(p / div) * E;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = rows[(size_t)s * E + i];
+    for (int i = threadIdx.x; i < E; i += blockDim.x) dst[i] = to_float(rows[(size_t)s * E + i]);
 }
 
 }  // namespace air
@@ -162,11 +163,13 @@ AIR_API int air_rows_by_index(const void* x, int dtype, const int* index, int di
     return 0;
 }
 
-AIR_API int air_planes_by_index(const float* rows, const int* index, int div, long long plane, float* out, int n, int E,
-                                cudaStream_t stream) {
+AIR_API int air_planes_by_index(const void* rows, int dtype, const int* index, int div, long long plane, float* out,
+                                int n, int E, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (div <= 0) return AIR_ERR_BAD_ARGUMENT;
-    return air::launch(air::planes_by_index_kernel, n, 256, 0, stream, rows, index, div, (size_t)plane, out, E);
+    AIR_DISPATCH(dtype, TT, return air::launch(air::planes_by_index_kernel<TT>, n, 256, 0, stream, (const TT*)rows, index,
+                                               div, (size_t)plane, out, E));
+    return 0;
 }
 
 AIR_API int air_moe_route(const float* z, int ld, int T, int n, int top, int score, int renormalize, int has_gate,

@@ -51,7 +51,7 @@ _SIGNATURES = {
                          c_void_p, c_longlong, c_longlong, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p, c_int,
                          c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "air_rows_by_index": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-    "air_planes_by_index": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
+    "air_planes_by_index": [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_void_p],
     "air_qkv_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                         c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p, c_void_p],
@@ -631,13 +631,13 @@ def rows_by_index(x, index, div, scale, out):
 
 
 def planes_by_index(rows, index, div, out):
-    """out[index[s] % div, index[s] // div] = rows[s]; rows float32 [n, E], out float32 [div, T, E]."""
+    """out[index[s] % div, index[s] // div] = rows[s]; rows [n, E], out float32 [div, T, E]."""
     n, E = rows.shape
-    _req(rows, "rows", (torch.float32,))
+    _req(rows, "rows", _FLOATS)
     _req(index, "index", _I32, (n,))
     _req(out, "out", (torch.float32,), (div, None, E))
-    _check(_get("air_planes_by_index")(rows.data_ptr(), index.data_ptr(), int(div), out.shape[1] * E, out.data_ptr(), n,
-                                       E, _stream()), "planes_by_index")
+    _check(_get("air_planes_by_index")(rows.data_ptr(), _DT[rows.dtype], index.data_ptr(), int(div), out.shape[1] * E,
+                                       out.data_ptr(), n, E, _stream()), "planes_by_index")
     return out
 
 

@@ -8,7 +8,7 @@ from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward, GatedSum
 from .linear import Linear
-from .mlp import SwiGLU, fused_gate_up_pays
+from .mlp import SwiGLU
 from .registry import register_feed_forward
 from .spec import PartSpec
 
@@ -37,12 +37,11 @@ class RoutedExperts(FeedForward):
     Everything happens on the device: a kernel picks the experts, one orders the (token, choice) pairs by expert, and
     two grouped products (gate and up with the activation; down) walk the experts' rows.  The outputs of a token's
     choices land in `top` planes that the norm behind the layer adds in order, so the sum does not depend on the
-    batch.  A step of many tokens that is not a decode step (so never part of a CUDA graph) instead reads the experts'
-    row counts on the host, once per layer, and runs every expert's rows through the dense feed-forward's products
-    (the tcgen05 kernel with the activation in its epilogue, the library's product for down): see HOST_ROWS."""
+    batch.  From LIBRARY_ROWS rows per expert (in the mean) on, a bfloat16 step hands the two products to the library's
+    grouped product (which also takes the experts' bounds from the device): there the experts' outputs are rounded to
+    bfloat16 before they are added up in 32-bit."""
 
-    # From so many rows per expert (in the mean) on, a bfloat16 step that holds prompt portions takes the road over the host.
-    HOST_ROWS = 64
+    LIBRARY_ROWS = 32
 
     graph_safe = True
 
@@ -101,8 +100,6 @@ class RoutedExperts(FeedForward):
         self.down = torch.stack([tensors[f"{p}e{i}.down"] for i in range(n)]).contiguous()      # [n, E, F]
         if self.gate_up.dtype != rt.dtype:
             raise ValueError(f"{p}: the experts are stored as {self.gate_up.dtype}, the engine computes in {rt.dtype}")
-        self.gate_up_of = [Linear(self.gate_up[i], rt.status, gate_up_block=block if block != F else 0) for i in range(n)]
-        self.down_of = [Linear(self.down[i], rt.status) for i in range(n)]
         if self.shared is not None:
             self.shared.load(tensors, rt)
 
@@ -121,8 +118,8 @@ class RoutedExperts(FeedForward):
         tiles, num_tiles = ints[n + 1 + pairs:-1].view(-1, 2), ints[-1:]
         ops.moe_sort(expert, n, start, pair_of_slot, tiles, num_tiles)
         y = torch.empty((top, T, E), dtype=torch.float32, device=dev)
-        if x.dtype == torch.bfloat16 and not ctx.all_decode and pairs >= self.HOST_ROWS * n:
-            self._experts_one_by_one(x, start, pair_of_slot, weight, y)
+        if x.dtype == torch.bfloat16 and pairs >= self.LIBRARY_ROWS * n and E % 16 == 0 and F % 16 == 0:
+            self._experts_by_the_library(x, start, pair_of_slot, weight, y)
         else:
             act = torch.empty((pairs, F), dtype=x.dtype, device=dev)
             ops.grouped_gemm(x, self.gate_up, act, F, E, lda=E, ldo=F, groups=n, a_index=pair_of_slot, a_div=top,
@@ -134,27 +131,14 @@ class RoutedExperts(FeedForward):
             return y
         return GatedSum(y, self.shared.forward(x, ctx), gate)
 
-    def _experts_one_by_one(self, x, start, pair_of_slot, weight, y):
-        """The road over the host: the rows in the experts' order with their weights on them, every expert's rows through
-        the products of the dense gated feed-forward, the results back to the planes."""
+    def _experts_by_the_library(self, x, start, pair_of_slot, weight, y):
+        """The road of steps with many rows per expert: the rows in the experts' order with their weights on them, the
+        library's grouped product (it takes the experts' bounds from the device) for gate and up, the package's
+        activation kernel, the grouped product for down, the results back to the planes."""
         top, (T, E) = self.top, x.shape
         pairs = T * top
         rows = ops.rows_by_index(x, pair_of_slot, top, weight.view(-1), torch.empty((pairs, E), dtype=x.dtype, device=x.device))
-        outs = torch.empty((pairs, E), dtype=torch.float32, device=x.device)
-        bounds = start.tolist()              # the one read of the device per layer
-        for e in range(self.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi == lo:
-                continue
-            mine, gate_up, down = rows[lo:hi], self.gate_up_of[e], self.down_of[e]
-            if gate_up.gate_up_block and (gate_up.small(mine) or fused_gate_up_pays(hi - lo, gate_up.out_features)):
-                act = gate_up.silu_mul(mine)
-            else:
-                act = torch.empty((hi - lo, self.inter), dtype=x.dtype, device=x.device)
-                ops.silu_mul(gate_up(mine, x.dtype), act, block=self.block)
-            if down.small(act):
-                outs[lo:hi].zero_()
-                ops.add_parts(outs[lo:hi], down.partial(act))
-            else:
-                torch.mm(act, down.weight.t(), out_dtype=torch.float32, out=outs[lo:hi])
-        ops.planes_by_index(outs, pair_of_slot, top, y)
+        ends = start[1:].clone()
+        act = torch.empty((pairs, self.inter), dtype=x.dtype, device=x.device)
+        ops.silu_mul(torch._grouped_mm(rows, self.gate_up.transpose(1, 2), offs=ends), act, block=self.block)
+        ops.planes_by_index(torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_of_slot, top, y)

@@ -24,7 +24,7 @@ class PortionAttention:
     The mixer offers: rt, heads, kv_heads (1 for a latent), scale, window, chunk, and sinks (float32 [heads] or None)."""
 
     PORTION = 32
-    BLOCK = 512
+    BLOCK = 1024
     PLAN = "attention.portions"
 
     def plan_key(self):

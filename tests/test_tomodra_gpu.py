@@ -371,12 +371,11 @@ def test_unequal_requests_together_with_pages_and_slots_used_again(name, dtype, 
 
 
 @pytest.mark.parametrize("name", ["A", "B", "C"])
-def test_experts_one_by_one_over_the_host(name, monkeypatch):
-    """The road that steps of many tokens take through the experts (row counts read on the host, every expert's rows
-    through the dense feed-forward's products), forced for short prompts too; experts that nobody chose, experts with
-    one row, mixed batches."""
+def test_experts_through_the_librarys_grouped_product(name, monkeypatch):
+    """The road that steps of many rows per expert take through the experts, forced for short prompts too; experts that
+    nobody chose, experts with one row, mixed batches."""
     from air_b200.parts.experts import RoutedExperts
-    monkeypatch.setattr(RoutedExperts, "HOST_ROWS", 1)
+    monkeypatch.setattr(RoutedExperts, "LIBRARY_ROWS", 0)
     streams = streams_for(name, 70, (3, 150, 41))
     got, _ = replay(name, "bfloat16", util.trace_whole(streams), page_tokens=64)
     tu.check(got, name, streams, "bfloat16")
