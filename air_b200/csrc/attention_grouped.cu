@@ -6,9 +6,11 @@
 // grouped_attention_kernel<T, JB>: block (token, key/value head and block of JB query heads of its group, split).  Keys
 //   are visited in tiles of 64 aligned to absolute positions; split s of S takes the tiles whose index is s modulo S.
 //   A tile's rows (and its values, unless the values are the keys' first columns) are staged in shared memory with
-//   16-byte loads, rows padded to an odd number of words.  Scores: a thread takes one key and JB / 4 heads, the queries
-//   wait in shared memory as float32.  Softmax: online, one warp per head in turn, 32-bit.  Weighted values: a thread
-//   takes columns tid, tid + 256, .. for all JB heads.  The block writes unnormalised sums, its maximum and its sum of
+//   16-byte loads, rows padded to an odd number of words.  Scores: a thread takes one key, JB / 2 heads and half of the
+//   row's words; the queries wait in shared memory as float32, a word's heads side by side, so that a thread fetches
+//   its heads' numbers 16 bytes at a time.  Softmax: online, one warp per head in turn, 32-bit.  Weighted values: a
+//   thread takes the words tid, tid + 256, .. of the value rows for all JB heads, whose weights it fetches 16 bytes at
+//   a time.  The block writes unnormalised sums, its maximum and its sum of
 //   weights; grouped_combine_kernel merges the splits in order, adds the sink's term to the denominator and rounds
 //   once.  What a query computes depends on its position, the split count and the cache only.
 //
@@ -18,11 +20,25 @@
 
 namespace air {
 
-constexpr int GA_KT = 64, GA_NI = 3;      // keys per tile; columns per thread (dv up to 256 * GA_NI)
+constexpr int GA_KT = 64;                 // keys per tile
 
-template <typename T> struct Words;       // how elements lie in 32-bit words
-template <> struct Words<float> { static constexpr int per = 1; };
-template <> struct Words<__nv_bfloat16> { static constexpr int per = 2; };
+template <typename T> struct Words;       // how elements lie in 32-bit words, and how many words of a value row a
+template <> struct Words<float> { static constexpr int per = 1, ni = 3; };             // thread takes (rows of up to
+template <> struct Words<__nv_bfloat16> { static constexpr int per = 2, ni = 2; };     // 256 * ni words)
+
+// n floats (2, 4, 8 or 16) from shared memory, the address aligned to min(16, 4 n) bytes
+template <int N> __device__ __forceinline__ void load_floats(const float* p, float (&v)[N]) {
+    if constexpr (N == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        v[0] = t.x; v[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            const float4 t = *reinterpret_cast<const float4*>(p + 4 * i);
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    }
+}
 
 template <typename T, int JB>
 __global__ void __launch_bounds__(256)
@@ -30,7 +46,7 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
                          const int* __restrict__ positions, float* __restrict__ part, int H, int G, int d, int dv, int P,
                          int window, int mask_mode, float scale, int latent, int splits) {
-    constexpr int JT = JB / 4, PER = Words<T>::per;
+    constexpr int JT = JB / 2, PER = Words<T>::per, NI = Words<T>::ni;
     extern __shared__ __align__(16) float smem[];
     pdl_enter(TR_ATT_GROUPED);
     const int t = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -43,9 +59,12 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
     const int* bt = block_table + (size_t)slot * max_blocks;
     const int kw = d / PER, vw = dv / PER;                 // words per row
     const int ksw = kw | 1, vsw = vw | 1;                  // ... as staged: odd, so that rows fall into different banks
-    float* qs = smem;                                      // [JB][d]
-    float* S = qs + JB * d;                                // [JB][64]
-    float* corr = S + JB * GA_KT;                          // [JB], then the running maximum and sum
+    // The queries lie word by word, all heads of a word together: [kw][JB][PER] floats, so that a thread's heads are
+    // one or a few 16-byte loads.  The scores and then the weights lie key by key: [2][64][JB] (two halves of the dot
+    // products' range, added up by the softmax; the weights in the first half).
+    float* qs = smem;
+    float* S = qs + JB * d;
+    float* corr = S + 2 * GA_KT * JB;                      // [JB], then the running maximum and sum
     float* mrun = corr + JB;
     float* lrun = mrun + JB;
     int* pages = reinterpret_cast<int*>(lrun + JB);        // [64]: the page of each of the tile's keys
@@ -59,14 +78,16 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
             const size_t at = ((size_t)t * H + head0 + j) * d + e;
             v = q_f32 ? ((const float*)q_any)[at] : to_float(((const T*)q_any)[at]);
         }
-        qs[i] = v;
+        qs[((e / PER) * JB + j) * PER + e % PER] = v;
     }
     if (tid < JB) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }
-    float acc[JB][GA_NI];
+    float acc[JB][NI][PER];
 #pragma unroll
     for (int j = 0; j < JB; ++j)
 #pragma unroll
-        for (int i = 0; i < GA_NI; ++i) acc[j][i] = 0.f;
+        for (int i = 0; i < NI; ++i)
+#pragma unroll
+            for (int e = 0; e < PER; ++e) acc[j][i][e] = 0.f;
     const size_t page_stride = latent ? (size_t)P * d : (size_t)G * P * (d + dv);
     const int kchunks = d * (int)sizeof(T) / 16, vchunks = dv * (int)sizeof(T) / 16;
     for (int kt = lo / GA_KT + split; kt * GA_KT <= pos; kt += splits) {
@@ -79,11 +100,11 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
         __syncthreads();
 #pragma unroll 4
         for (int c = tid; c < GA_KT * kchunks; c += 256) {
-            const int r = c / kchunks, cc = c % kchunks, key = key0 + r;
+            const int r = c / kchunks, cc = c % kchunks;
             uint4 v = make_uint4(0, 0, 0, 0);
             if (pages[r] >= 0) {
                 const T* row = cache + (size_t)pages[r] * page_stride +
-                               (latent ? (size_t)(key % P) * d : ((size_t)g * P + key % P) * d);
+                               (latent ? (size_t)((key0 + r) % P) * d : ((size_t)g * P + (key0 + r) % P) * d);
                 v = *reinterpret_cast<const uint4*>(row + cc * (16 / sizeof(T)));
             }
             uint32_t* dst = Kw + r * ksw + cc * 4;
@@ -92,47 +113,48 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
         if (!latent)
 #pragma unroll 4
             for (int c = tid; c < GA_KT * vchunks; c += 256) {
-                const int r = c / vchunks, cc = c % vchunks, key = key0 + r;
+                const int r = c / vchunks, cc = c % vchunks;
                 uint4 v = make_uint4(0, 0, 0, 0);
                 if (pages[r] >= 0) {
                     const T* row = cache + (size_t)pages[r] * page_stride + (size_t)G * P * d +
-                                   ((size_t)g * P + key % P) * dv;
+                                   ((size_t)g * P + (key0 + r) % P) * dv;
                     v = *reinterpret_cast<const uint4*>(row + cc * (16 / sizeof(T)));
                 }
                 uint32_t* dst = Vw + r * vsw + cc * 4;
                 dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
             }
         __syncthreads();
-        {   // scores: key kk, heads gq * JT ..
-            const int kk = tid & 63, gq = tid >> 6;
+        {   // scores: key kk, heads gq * JT .., half of the row's words
+            const int kk = tid & 63, gq = (tid >> 6) & 1, half = tid >> 7;
             float s[JT];
 #pragma unroll
             for (int jt = 0; jt < JT; ++jt) s[jt] = 0.f;
             const uint32_t* krow = Kw + kk * ksw;
-            for (int w = 0; w < kw; ++w) {
+            const int w1 = (half + 1) * (kw / 2);
+#pragma unroll 2
+            for (int w = half * (kw / 2); w < w1; ++w) {
                 const uint32_t word = krow[w];
+                float qv[JT * PER];
+                load_floats<JT * PER>(qs + (w * JB + gq * JT) * PER, qv);
                 if (PER == 2) {
                     const __nv_bfloat162 k2 = *reinterpret_cast<const __nv_bfloat162*>(&word);
                     const float k0 = __low2float(k2), k1 = __high2float(k2);
 #pragma unroll
-                    for (int jt = 0; jt < JT; ++jt) {
-                        const float2 q2 = *reinterpret_cast<const float2*>(qs + (gq * JT + jt) * d + 2 * w);
-                        s[jt] = fmaf(k1, q2.y, fmaf(k0, q2.x, s[jt]));
-                    }
+                    for (int jt = 0; jt < JT; ++jt) s[jt] = fmaf(k1, qv[jt * PER + PER - 1], fmaf(k0, qv[jt * PER], s[jt]));
                 } else {
                     const float k0 = __uint_as_float(word);
 #pragma unroll
-                    for (int jt = 0; jt < JT; ++jt) s[jt] = fmaf(k0, qs[(gq * JT + jt) * d + w], s[jt]);
+                    for (int jt = 0; jt < JT; ++jt) s[jt] = fmaf(k0, qv[jt], s[jt]);
                 }
             }
-            const int key = key0 + kk;
-            const bool seen = key >= lo && key <= pos;
 #pragma unroll
-            for (int jt = 0; jt < JT; ++jt) S[(gq * JT + jt) * GA_KT + kk] = seen ? s[jt] * scale : -INFINITY;
+            for (int jt = 0; jt < JT; ++jt) S[(half * GA_KT + kk) * JB + gq * JT + jt] = s[jt];
         }
         __syncthreads();
         for (int j = warp; j < JB; j += 8) {
-            const float s0 = S[j * GA_KT + lane], s1 = S[j * GA_KT + lane + 32];
+            const bool seen0 = key0 + lane >= lo && key0 + lane <= pos, seen1 = key0 + lane + 32 >= lo && key0 + lane + 32 <= pos;
+            const float s0 = seen0 ? (S[lane * JB + j] + S[(GA_KT + lane) * JB + j]) * scale : -INFINITY;
+            const float s1 = seen1 ? (S[(lane + 32) * JB + j] + S[(GA_KT + lane + 32) * JB + j]) * scale : -INFINITY;
             const float m_old = mrun[j];
             const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
             float p0 = 0.f, p1 = 0.f, c = 1.f;
@@ -142,8 +164,8 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
                 c = expf(m_old - m_new);
             }
             const float sum = warp_sum(p0 + p1);
-            S[j * GA_KT + lane] = p0;
-            S[j * GA_KT + lane + 32] = p1;
+            S[lane * JB + j] = p0;
+            S[(lane + 32) * JB + j] = p1;
             if (lane == 0) { lrun[j] = lrun[j] * c + sum; mrun[j] = m_new; corr[j] = c; }
         }
         __syncthreads();
@@ -151,21 +173,31 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
         for (int j = 0; j < JB; ++j) {
             const float c = corr[j];
 #pragma unroll
-            for (int i = 0; i < GA_NI; ++i) acc[j][i] *= c;
+            for (int i = 0; i < NI; ++i)
+#pragma unroll
+                for (int e = 0; e < PER; ++e) acc[j][i][e] *= c;
         }
-        const T* Vt = reinterpret_cast<const T*>(Vw);
         for (int kk = 0; kk < GA_KT; ++kk) {
-            float v[GA_NI];
+            float pv[JB];
+            load_floats<JB>(S + kk * JB, pv);
 #pragma unroll
-            for (int i = 0; i < GA_NI; ++i) {
-                const int c = tid + 256 * i;
-                v[i] = c < dv ? to_float(Vt[(size_t)kk * vstride * PER + c]) : 0.f;
-            }
+            for (int i = 0; i < NI; ++i) {
+                const int w = tid + 256 * i;
+                if (w >= vw) continue;
+                const uint32_t word = Vw[kk * vstride + w];
+                if (PER == 2) {
+                    const __nv_bfloat162 v2 = *reinterpret_cast<const __nv_bfloat162*>(&word);
+                    const float v0 = __low2float(v2), v1 = __high2float(v2);
 #pragma unroll
-            for (int j = 0; j < JB; ++j) {
-                const float p = S[j * GA_KT + kk];
+                    for (int j = 0; j < JB; ++j) {
+                        acc[j][i][0] = fmaf(pv[j], v0, acc[j][i][0]);
+                        acc[j][i][PER - 1] = fmaf(pv[j], v1, acc[j][i][PER - 1]);
+                    }
+                } else {
+                    const float v0 = __uint_as_float(word);
 #pragma unroll
-                for (int i = 0; i < GA_NI; ++i) acc[j][i] = fmaf(p, v[i], acc[j][i]);
+                    for (int j = 0; j < JB; ++j) acc[j][i][0] = fmaf(pv[j], v0, acc[j][i][0]);
+                }
             }
         }
     }
@@ -175,9 +207,11 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
         if (j >= nj) continue;
         float* dst = part + (((size_t)t * H + head0 + j) * splits + split) * (dv + 2);
 #pragma unroll
-        for (int i = 0; i < GA_NI; ++i) {
-            const int c = tid + 256 * i;
-            if (c < dv) dst[c] = acc[j][i];
+        for (int i = 0; i < NI; ++i) {
+            const int w = tid + 256 * i;
+            if (w >= vw) continue;
+#pragma unroll
+            for (int e = 0; e < PER; ++e) dst[w * PER + e] = acc[j][i][e];
         }
         if (tid == 0) { dst[dv] = mrun[j]; dst[dv + 1] = lrun[j]; }
     }
@@ -215,7 +249,7 @@ int launch_grouped(const void* q, int q_f32, const void* cache, const int* block
                    int window, int mask_mode, float scale, int latent, int splits, cudaStream_t stream) {
     constexpr int PER = Words<T>::per;
     const int ksw = (d / PER) | 1, vsw = (dv / PER) | 1;
-    const size_t smem = sizeof(float) * ((size_t)JB * d + JB * GA_KT + 3 * JB + GA_KT) +
+    const size_t smem = sizeof(float) * ((size_t)JB * d + 2 * JB * GA_KT + 3 * JB + GA_KT) +
                         4 * (size_t)GA_KT * (ksw + (latent ? 0 : vsw));
     if (smem > 227 * 1024) return AIR_ERR_BAD_ARGUMENT;
     auto kernel = grouped_attention_kernel<T, JB>;
@@ -235,7 +269,7 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
                                   const float* sink, int latent, int splits, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int bytes = dtype == AIR_F32 ? 4 : 2;
-    if (d <= 0 || dv <= 0 || dv > 256 * air::GA_NI || (d * bytes) % 16 || (dv * bytes) % 16 || H <= 0 || G <= 0 ||
+    if (d <= 0 || dv <= 0 || dv > (dtype == AIR_F32 ? 768 : 1024) || (d * bytes) % 16 || (dv * bytes) % 16 || H <= 0 || G <= 0 ||
         H % G || splits <= 0 || splits > 65535 || mask_mode < 0 || mask_mode > 1 || (latent && (dv > d || G != 1)))
         return AIR_ERR_BAD_ARGUMENT;
     const int J = H / G;

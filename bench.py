@@ -667,6 +667,162 @@ def design_kernels(width, heads, kv_heads, ff, T, batch, context):
     return rows
 
 
+def tomodra_kernels(width, heads, kv_heads, ff, T, batch, context):
+    """Tomodra's kernels alone at the layer's shapes beside the like kernel of the Qwen2 decoder, from memory (512 MB
+    written before each launch, the writes' own time subtracted): microseconds, and the share of the measured copy
+    rate (bytes) or of the measured bf16 rate (flops) that the algorithm's bytes or flops make."""
+    import torch
+    from types import SimpleNamespace
+    from air_b200.csrc import ops
+    from air_b200.parts.base import HostBatch, Runtime
+    from air_b200.parts.gathered_attention import PortionAttention
+    from air_b200.parts.rope import bent_frequencies
+    pk = peaks()
+    big = torch.empty(512 << 20, dtype=torch.uint8, device="cuda")
+
+    def graph_time(calls, reps=5):
+        for c in calls:
+            c()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(reps):
+                for c in calls:
+                    c()
+        graph.replay()
+        torch.cuda.synchronize()
+        us = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            us.append(a.elapsed_time(b) * 1e3 / reps)
+        return statistics.median(us)
+
+    flush = lambda: big.zero_()
+    t_flush = graph_time([flush])
+    rows = []
+
+    def report(name, f, nbytes=0, flops=0):
+        us = graph_time([flush, f]) - t_flush
+        frac = (nbytes / us / 1e3 / pk["hbm_gbs"]) if nbytes else (flops / us / 1e6 / pk["bf16_tflops"])
+        rows.append({"kernel": name, "us": round(us, 1), "of": "copy rate" if nbytes else "bf16 rate", "frac": round(frac, 3)})
+        print(f"  {name:64s} {us:8.1f} us  {frac:5.2f} of the measured {'copy' if nbytes else 'bf16'} rate", flush=True)
+
+    E, H, G, d, P = width, heads, kv_heads, 128, 64
+    R, rot, window = 512, 64, 1024
+    n_exp, top, F = 16, 2, ff // 4
+    dev, f32, bf = "cuda", torch.float32, torch.bfloat16
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    freq = bent_frequencies(rot, 5e5, None)[0].to(dev)
+    for label, n_rows, entries in (("prompt", T, [(0, T)]), ("decode", batch, [(context, 1)] * batch)):
+        print(f"{label}: {n_rows} rows, width {E}, {H} heads, latent {R} + {rot}, window {window}, {n_exp} experts of {F}, top {top}")
+        S = len(entries)
+        positions = torch.cat([torch.arange(p, p + n, dtype=torch.int32) for p, n in entries]).to(dev)
+        seq = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, (_, n) in enumerate(entries)]).to(dev)
+        per_request = -(-(max(p + n for p, n in entries)) // P)
+        bt = torch.arange(S * per_request, dtype=torch.int32, device=dev).view(S, per_request).contiguous()
+        N = n_rows
+        # ---- the norm behind the sum, beside the norm before the sub-layer
+        h, delta = torch.randn(N, E, device=dev), torch.randn(N, E, device=dev)
+        w, x16 = torch.ones(E, device=dev, dtype=bf), torch.empty(N, E, device=dev, dtype=bf)
+        report("post_norm (stream, a float32 sum in; stream and rows out)", lambda: ops.post_norm(h, 3.0, delta, None, None, w, 1e-5, x16), N * E * 14)
+        report("  Qwen2: add_rmsnorm", lambda: ops.add_rmsnorm(h, delta, w, 1e-5, x16), N * E * 14)
+        # ---- from the first projection to queries and the latent's pages
+        proj = torch.randn(N, H * (d + rot) + R + rot, device=dev)
+        cw = torch.ones(R, device=dev)
+        rows_ = torch.zeros(S * per_request, P, R + rot, device=dev, dtype=bf).normal_(0, 0.5)
+        q_plain, q_full = torch.empty(N, H, d, device=dev, dtype=bf), torch.empty(N, H, R + rot, device=dev)
+        report("latent_prepare (norm of the latent, rotation, page write)", lambda: ops.latent_prepare(proj, cw, 1e-5, freq, positions, seq, bt, q_plain, q_full, rows_, True),
+               N * (proj.shape[1] * 4 + H * d * 2 + H * rot * 4 + (R + rot) * 2))
+        Wq = (H + 2 * G) * d
+        qkv = torch.randn(N, Wq, device=dev)
+        qn, q16 = torch.ones(d, device=dev), torch.empty(N, H, d, device=dev, dtype=bf)
+        kvc = torch.zeros(S * per_request, 2 * G * P * d, device=dev, dtype=bf).normal_(0, 0.5)
+        f2 = bent_frequencies(64, 1e4, {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0})[0].to(dev)
+        report("qk_normed_prepare (norm per head, rotation, page write)", lambda: ops.qk_normed_prepare(qkv, qn, qn, 1e-5, f2, "neighbours", 1.2, positions, seq, bt, q16, kvc, G, d, P),
+               N * Wq * 6)
+        table = torch.randn(context + T + 8, d, device=dev)
+        kv5 = kvc.view(-1, 2, G, P, d)
+        report("  Qwen2: qkv_rope_store", lambda: ops.qkv_rope_store(qkv, None, table, positions, seq, bt, q16, kv5, H, G, d), N * Wq * 6)
+        # ---- the products per head around latent attention
+        uk_t = torch.randn(H, R, d, device=dev, dtype=bf)
+        report("grouped product: queries through the key expansion", lambda: ops.grouped_gemm(q_plain, uk_t, q_full, R, d, lda=H * d, ldo=H * (R + rot), groups=H, a_group_stride=d, o_group_stride=R + rot, a_local=True, o_local=True, rows_per_group=N),
+               flops=2 * N * H * d * R)
+        # ---- attention
+        summed = torch.empty(N, H, R, device=dev, dtype=bf)
+        out16 = torch.empty(N, H, d, device=dev, dtype=bf)
+        if label == "decode":
+            keys = min(window, context + 1)
+            report("grouped_attention, latent rows (all heads read a row once)", lambda: ops.grouped_attention(q_full, rows_, bt, seq, positions, summed, window, 0.07, latent=True),
+                   batch * keys * (R + rot) * 2)
+            sink = torch.zeros(H, device=dev)
+            report("grouped_attention, keys and values per head, chunk, sink", lambda: ops.grouped_attention(q16, kvc, bt, seq, positions, out16, None, 0.09, kv_heads=G, page_tokens=P, chunk=window, sink=sink),
+                   batch * (context % window + 1) * 2 * G * d * 2)
+            report("  Qwen2: decode_attention (all keys)", lambda: ops.decode_attention(q16, kv5, bt, seq, positions, out16, None, 0.09),
+                   batch * (context + 1) * 2 * G * d * 2)
+        else:
+            class Road(PortionAttention):
+                rt = Runtime(device=torch.device(dev), dtype=bf, page_tokens=P)
+                chunk, sinks = None, None
+            road = Road()
+            road.heads, road.window, road.scale = H, window, 0.07
+            plan = road.plan(HostBatch(counts=[T], lengths=[0], slots=[0], q_start=[0, T]))
+            ctx = SimpleNamespace(plans={road.plan_key(): SimpleNamespace(small_seq=i32(plan.arrays["small_seq"]), **plan.values)},
+                                  token_seq=seq, positions=positions)
+            pairs_seen = sum(min(window, t + 1) for t in range(T))
+            t0 = time.time()
+            us = []
+            for _ in range(5):
+                flush()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                road.attend(q_full, rows_, bt, ctx, summed, latent=True)
+                b.record()
+                torch.cuda.synchronize()
+                us.append(a.elapsed_time(b) * 1e3)
+            us = statistics.median(us[1:])
+            fl = 2 * pairs_seen * H * (2 * R + rot)
+            rows.append({"kernel": "portion attention over latent rows (gather, product, softmax, product)", "us": round(us, 1), "of": "bf16 rate", "frac": round(fl / us / 1e6 / pk["bf16_tflops"], 3)})
+            print(f"  {'portion attention over latent rows (gather, 2 products, softmax), launched from the host':64s} {us:8.1f} us  {fl / us / 1e6 / pk['bf16_tflops']:5.2f} of the measured bf16 rate (the flops of the keys that are seen)")
+            tiles = i32([[0, 16 * i, 16 * i, 16] for i in range(T // 16)])
+            report("  Qwen2: prefill_attention_tc (all keys, heads of 128)", lambda: ops.prefill_attention_tc(q16, kv5, bt, tiles, out16, None, 0.09),
+                   flops=2 * (T * (T + 1) // 2) * H * 2 * d)
+        # ---- the experts
+        x = torch.randn(N, E, device=dev, dtype=bf)
+        z = torch.randn(N, 24, device=dev)
+        expert = torch.empty(N, top, dtype=torch.int32, device=dev)
+        weight, gate = torch.empty(N, top, device=dev), torch.empty(N, device=dev)
+        pairs = N * top
+        start, slots_ = torch.empty(n_exp + 1, dtype=torch.int32, device=dev), torch.empty(pairs, dtype=torch.int32, device=dev)
+        tiles_, count = torch.empty(pairs // 64 + n_exp, 2, dtype=torch.int32, device=dev), torch.empty(1, dtype=torch.int32, device=dev)
+        report("moe_route + moe_sort", lambda: (ops.moe_route(z, n_exp, top, expert, weight, gate, has_gate=True), ops.moe_sort(expert, n_exp, start, slots_, tiles_, count)), N * 24 * 4 + pairs * 16)
+        gate_up, down = torch.randn(n_exp, 2 * F, E, device=dev, dtype=bf) * 0.02, torch.randn(n_exp, E, F, device=dev, dtype=bf) * 0.02
+        act, y = torch.empty(pairs, F, device=dev, dtype=bf), torch.empty(top, N, E, device=dev)
+        if label == "decode":
+            used = len(set(expert.flatten().tolist()))
+            report(f"grouped product: gate, up and activation of {used} experts", lambda: ops.grouped_gemm(x, gate_up, act, F, E, lda=E, ldo=F, groups=n_exp, a_index=slots_, a_div=top, a_scale=weight.view(-1), start=start, tiles=tiles_, num_tiles=count, silu_mul=True, gate_block=128),
+                   used * 2 * F * E * 2)
+            report(f"grouped product: down of {used} experts", lambda: ops.grouped_gemm(act, down, y, E, F, lda=F, ldo=E, groups=n_exp, o_index=slots_, o_div=top, o_part_stride=N * E, start=start, tiles=tiles_, num_tiles=count),
+                   used * F * E * 2)
+            dense = torch.randn(2 * ff, E, device=dev, dtype=bf) * 0.02
+            dact = torch.empty(N, ff, device=dev, dtype=bf)
+            report("  Qwen2: gate, up and activation (gemm_tc, dense, as wide as 4 experts)", lambda: ops.gemm_tc(x, dense, dact, 256, ops.EPI_SILU), 2 * ff * E * 2)
+        else:
+            xs = torch.empty(pairs, E, device=dev, dtype=bf)
+            ends = start[1:].clone()
+            report("experts: rows in order, library grouped product, activation", lambda: (ops.rows_by_index(x, slots_, top, weight.view(-1), xs), ops.silu_mul(torch._grouped_mm(xs, gate_up.transpose(1, 2), offs=ends), act, block=128)),
+                   flops=2 * pairs * 2 * F * E)
+            report("experts: library grouped product for down, rows back to planes", lambda: ops.planes_by_index(torch._grouped_mm(act, down.transpose(1, 2), offs=ends), slots_, top, y),
+                   flops=2 * pairs * F * E)
+            dense = torch.randn(2 * ff, E, device=dev, dtype=bf) * 0.02
+            dact = torch.empty(N, ff, device=dev, dtype=bf)
+            report("  Qwen2: gate, up and activation (gemm_tc, dense, the same flops)", lambda: ops.gemm_tc(x, dense, dact, 256, ops.EPI_SILU), flops=2 * N * 2 * ff * E)
+    return rows
+
+
 def design_bench(args):
     import torch
     from air_b200.engine.batch import Entry, LAST_SAMPLED
