@@ -17,6 +17,7 @@
 // q: [T, H, d] (float32, or the cache's type); cache: pages of keys [G, P, d] then values [G, P, dv], or (latent)
 // [P, d] whose first dv columns are the values; masks as in attention_ref.cu.  d and dv are multiples of 16 bytes.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace air {
 
@@ -217,6 +218,229 @@ grouped_attention_kernel(const void* __restrict__ q_any, int q_f32, const T* __r
     }
 }
 
+// grouped_attention_tc_kernel: the same block for a bfloat16 cache with both products on the tensor cores (m16n8k16,
+// 32-bit accumulators): the 16 query heads of the block are the rows of the instruction.  What the 32-bit kernel keeps in
+// float32 stays 32-bit in effect: a float32 query is split into two bfloat16 numbers (q = hi + lo, the products q.k
+// added in 32-bit), and so is every weight of the softmax before it meets the values; scores, maxima, sums and the
+// weights themselves are float32.  Scores: warp w takes keys 8w .. 8w + 7 of the tile; weighted values: warp w takes
+// the columns' eighth w; the values' fragments come transposed out of the staged rows (ldmatrix.trans).
+constexpr int GT_MAX_NT = 16;      // 8-column tiles of the values per warp: dv up to 1024
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int bytes = valid ? 16 : 0;             // 0: the 16 bytes are zero-filled, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+
+__global__ void __launch_bounds__(256)
+grouped_attention_tc_kernel(const void* __restrict__ q_any, int q_f32, const __nv_bfloat16* __restrict__ cache,
+                            const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
+                            const int* __restrict__ positions, float* __restrict__ part, int H, int G, int d, int dv,
+                            int P, int window, int mask_mode, float scale, int latent, int splits, int stages) {
+    constexpr int JB = 16, PLD = GA_KT + 8;
+    extern __shared__ __align__(16) float smem[];
+    pdl_enter(TR_ATT_GROUPED);
+    const int t = blockIdx.x, split = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int slot = token_seq[t];
+    if (slot < 0) return;
+    const int J = H / G, hbs = (J + JB - 1) / JB;
+    const int g = blockIdx.y / hbs, j0 = (blockIdx.y % hbs) * JB, nj = min(JB, J - j0), head0 = g * J + j0;
+    const int pos = positions[t];
+    const int lo = window > 0 ? (mask_mode == 1 ? pos - pos % window : max(0, pos - window + 1)) : 0;
+    const int* bt = block_table + (size_t)slot * max_blocks;
+    const int kld = d + 8, vld = latent ? kld : dv + 8;      // elements per staged row: 16 bytes of padding
+    float* S = smem;                                          // [16][64] scores
+    float* corr = S + JB * GA_KT;                             // [16], then the running maximum and sum
+    float* mrun = corr + JB;
+    float* lrun = mrun + JB;
+    int* pages = reinterpret_cast<int*>(lrun + JB);           // [2][64]
+    __nv_bfloat16* Qh = reinterpret_cast<__nv_bfloat16*>(pages + 2 * GA_KT);  // [16][kld] (and Ql behind it)
+    __nv_bfloat16* Ql = Qh + JB * kld;
+    __nv_bfloat16* Ph = Ql + JB * kld;                        // [16][72] weights, high and low halves
+    __nv_bfloat16* Pl = Ph + JB * PLD;
+    __nv_bfloat16* K0 = Pl + JB * PLD;                        // per stage: keys [64][kld], then values [64][vld]
+    const int stage_elems = GA_KT * kld + (latent ? 0 : GA_KT * vld);
+    for (int i = tid; i < JB * d; i += 256) {
+        const int j = i / d, e = i % d;
+        __nv_bfloat16 hi = __float2bfloat16_rn(0.f), lw = hi;
+        if (j < nj) {
+            const size_t at = ((size_t)t * H + head0 + j) * d + e;
+            if (q_f32) split_bf16(((const float*)q_any)[at], hi, lw);
+            else hi = ((const __nv_bfloat16*)q_any)[at];
+        }
+        Qh[j * kld + e] = hi;
+        Ql[j * kld + e] = lw;
+    }
+    if (tid < JB) { mrun[tid] = -INFINITY; lrun[tid] = 0.f; }
+    const int ntiles = (dv + 7) / 8, per_warp = (ntiles + 7) / 8;      // 8-column tiles of the values, and a warp's share
+    const int nt0 = warp * per_warp;
+    float acc[GT_MAX_NT][4];
+#pragma unroll
+    for (int n = 0; n < GT_MAX_NT; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+    const size_t page_stride = latent ? (size_t)P * d : (size_t)G * P * (d + dv);
+    const int kchunks = d / 8, vchunks = dv / 8;
+    const int gq = lane >> 2, tq = lane & 3;
+    const uint32_t qh_addr = (uint32_t)__cvta_generic_to_shared(Qh), ql_addr = (uint32_t)__cvta_generic_to_shared(Ql);
+    const uint32_t ph_addr = (uint32_t)__cvta_generic_to_shared(Ph), pl_addr = (uint32_t)__cvta_generic_to_shared(Pl);
+    // ldmatrix.x4 of a 16 x 16 block of A (rows = heads): lane l gives the address of row l % 16, columns 8 (l / 16) ..
+    const int a_row = lane & 15, a_col = (lane >> 4) * 8;
+    // A tile's rows are brought by cp.async (16 bytes each, rows outside the mask zero-filled).  With two stages the
+    // next tile of this block is on its way while this one is used.
+    auto bring = [&](int key0, int buf) {
+        __nv_bfloat16* Kt = K0 + (size_t)buf * stage_elems;
+        __nv_bfloat16* Vt = Kt + GA_KT * kld;
+        const int* pg = pages + buf * GA_KT;
+        for (int c = tid; c < GA_KT * kchunks; c += 256) {
+            const int r = c / kchunks, cc = c % kchunks, page = pg[r];
+            const __nv_bfloat16* row = cache + (size_t)max(page, 0) * page_stride +
+                                       (latent ? (size_t)((key0 + r) % P) * d : ((size_t)g * P + (key0 + r) % P) * d);
+            cp_async16(Kt + r * kld + cc * 8, row + cc * 8, page >= 0);
+        }
+        if (!latent)
+            for (int c = tid; c < GA_KT * vchunks; c += 256) {
+                const int r = c / vchunks, cc = c % vchunks, page = pg[r];
+                const __nv_bfloat16* row = cache + (size_t)max(page, 0) * page_stride + (size_t)G * P * d +
+                                           ((size_t)g * P + (key0 + r) % P) * dv;
+                cp_async16(Vt + r * vld + cc * 8, row + cc * 8, page >= 0);
+            }
+        cp_async_commit();
+    };
+    auto look_up = [&](int key0, int buf) {
+        if (tid < GA_KT) {
+            const int key = key0 + tid;
+            pages[buf * GA_KT + tid] = key >= lo && key <= pos ? bt[key / P] : -1;
+        }
+    };
+    const int kt_first = lo / GA_KT + split;
+    if (stages == 2 && kt_first * GA_KT <= pos) {
+        look_up(kt_first * GA_KT, 0);
+        __syncthreads();
+        bring(kt_first * GA_KT, 0);
+    }
+    int turn = 0;
+    for (int kt = kt_first; kt * GA_KT <= pos; kt += splits, ++turn) {
+        const int key0 = kt * GA_KT;
+        const int buf = stages == 2 ? (turn & 1) : 0;
+        if (stages == 2) {
+            const int next = (kt + splits) * GA_KT;
+            if (next <= pos) {
+                look_up(next, buf ^ 1);
+                __syncthreads();
+                bring(next, buf ^ 1);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+        } else {
+            look_up(key0, 0);
+            __syncthreads();
+            bring(key0, 0);
+            cp_async_wait<0>();
+        }
+        __syncthreads();                                   // this tile's rows have landed, everybody's copies
+        const __nv_bfloat16* Kt = K0 + (size_t)buf * stage_elems;
+        const uint32_t vt_addr = (uint32_t)__cvta_generic_to_shared(latent ? Kt : Kt + GA_KT * kld);
+        {   // scores of the keys 8 warp .. 8 warp + 7
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            const __nv_bfloat16* krow = Kt + (8 * warp + gq) * kld + 2 * tq;
+            for (int kk = 0; kk < d; kk += 16) {
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + kk);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + kk + 8);
+                uint32_t a[4];
+                ldmatrix_x4(a, qh_addr + (a_row * kld + kk + a_col) * 2);
+                mma_bf16_16816(c, a[0], a[1], a[2], a[3], b0, b1);
+                if (q_f32) {
+                    ldmatrix_x4(a, ql_addr + (a_row * kld + kk + a_col) * 2);
+                    mma_bf16_16816(c, a[0], a[1], a[2], a[3], b0, b1);
+                }
+            }
+            S[gq * GA_KT + 8 * warp + 2 * tq] = c[0];
+            S[gq * GA_KT + 8 * warp + 2 * tq + 1] = c[1];
+            S[(gq + 8) * GA_KT + 8 * warp + 2 * tq] = c[2];
+            S[(gq + 8) * GA_KT + 8 * warp + 2 * tq + 1] = c[3];
+        }
+        __syncthreads();
+        for (int j = warp; j < JB; j += 8) {
+            const bool seen0 = key0 + lane >= lo && key0 + lane <= pos, seen1 = key0 + lane + 32 >= lo && key0 + lane + 32 <= pos;
+            const float s0 = seen0 ? S[j * GA_KT + lane] * scale : -INFINITY;
+            const float s1 = seen1 ? S[j * GA_KT + lane + 32] * scale : -INFINITY;
+            const float m_old = mrun[j];
+            const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+            float p0 = 0.f, p1 = 0.f, c = 1.f;
+            if (m_new != -INFINITY) {
+                p0 = expf(s0 - m_new);
+                p1 = expf(s1 - m_new);
+                c = expf(m_old - m_new);
+            }
+            const float sum = warp_sum(p0 + p1);
+            split_bf16(p0, Ph[j * PLD + lane], Pl[j * PLD + lane]);
+            split_bf16(p1, Ph[j * PLD + lane + 32], Pl[j * PLD + lane + 32]);
+            if (lane == 0) { lrun[j] = lrun[j] * c + sum; mrun[j] = m_new; corr[j] = c; }
+        }
+        __syncthreads();
+        {   // weighted values: the columns 8 nt0 .. of this warp
+            const float c_lo = corr[gq], c_hi = corr[gq + 8];
+#pragma unroll
+            for (int n = 0; n < GT_MAX_NT; ++n) {
+                acc[n][0] *= c_lo; acc[n][1] *= c_lo; acc[n][2] *= c_hi; acc[n][3] *= c_hi;
+            }
+#pragma unroll
+            for (int ks = 0; ks < GA_KT / 16; ++ks) {
+                uint32_t ah[4], al[4];
+                ldmatrix_x4(ah, ph_addr + (a_row * PLD + ks * 16 + a_col) * 2);
+                ldmatrix_x4(al, pl_addr + (a_row * PLD + ks * 16 + a_col) * 2);
+                // the values' fragments, two column tiles at a time: lane l gives the address of key ks * 16 + (l / 8 % 2) * 8
+                // + l % 8 at column 8 (tile + l / 16)
+                const int v_key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+                for (int n = 0; n < GT_MAX_NT; n += 2) {
+                    if (n >= per_warp || nt0 + n >= ntiles) break;
+                    const int col = 8 * (nt0 + n + (lane >> 4));
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, vt_addr + (v_key * vld + min(col, vld - 8)) * 2);
+                    mma_bf16_16816(acc[n], ah[0], ah[1], ah[2], ah[3], b[0], b[1]);
+                    mma_bf16_16816(acc[n], al[0], al[1], al[2], al[3], b[0], b[1]);
+                    if (n + 1 < per_warp && nt0 + n + 1 < ntiles) {
+                        mma_bf16_16816(acc[n + 1], ah[0], ah[1], ah[2], ah[3], b[2], b[3]);
+                        mma_bf16_16816(acc[n + 1], al[0], al[1], al[2], al[3], b[2], b[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();                                   // the tile has been used: its stage may be refilled
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < GT_MAX_NT; ++n) {
+        if (n >= per_warp || nt0 + n >= ntiles) continue;
+        const int col = 8 * (nt0 + n) + 2 * tq;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int j = gq + 8 * half;
+            if (j >= nj) continue;
+            float* dst = part + (((size_t)t * H + head0 + j) * splits + split) * (dv + 2);
+            if (col < dv) dst[col] = acc[n][2 * half];
+            if (col + 1 < dv) dst[col + 1] = acc[n][2 * half + 1];
+        }
+    }
+    if (tid < nj) {
+        float* dst = part + (((size_t)t * H + head0 + tid) * splits + split) * (dv + 2);
+        dst[dv] = mrun[tid];
+        dst[dv + 1] = lrun[tid];
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 grouped_combine_kernel(const float* __restrict__ part, const int* __restrict__ token_seq, const float* __restrict__ sink,
@@ -274,6 +498,26 @@ AIR_API int air_grouped_attention(const void* q, int q_f32, const void* cache, i
         return AIR_ERR_BAD_ARGUMENT;
     const int J = H / G;
     int rc = 0;
+    if (dtype == AIR_BF16 && d % 16 == 0 && dv % 8 == 0 && dv <= 128 * air::GT_MAX_NT / 2 * 1) {
+        // both products on the tensor cores
+        const int kld = d + 8, vld = dv + 8;
+        const size_t stage = 2 * ((size_t)air::GA_KT * kld + (latent ? 0 : (size_t)air::GA_KT * vld));
+        const size_t fixed = sizeof(float) * (16 * air::GA_KT + 3 * 16 + 2 * air::GA_KT) +
+                             2 * ((size_t)2 * 16 * kld + 2 * 16 * (air::GA_KT + 8));
+        const int stages = fixed + 2 * stage <= 227 * 1024 ? 2 : 1;
+        const size_t smem = fixed + stages * stage;
+        if (smem <= 227 * 1024) {
+            auto kernel = air::grouped_attention_tc_kernel;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            dim3 grid(T, G * ((J + 15) / 16), splits);
+            rc = air::launch(kernel, grid, 256, smem, stream, q, q_f32, (const __nv_bfloat16*)cache, block_table,
+                             max_blocks, token_seq, positions, part, H, G, d, dv, P, window, mask_mode, scale, latent,
+                             splits, stages);
+            if (rc) return rc;
+            return air::launch(air::grouped_combine_kernel<__nv_bfloat16>, dim3(T, H), 128, 0, stream, part, token_seq,
+                               sink, (__nv_bfloat16*)out, H, dv, splits);
+        }
+    }
     AIR_DISPATCH(dtype, TT, {
         if (J > 4)
             rc = air::launch_grouped<TT, 16>(q, q_f32, cache, block_table, max_blocks, token_seq, positions, part, T, H,
