@@ -383,6 +383,31 @@ def test_experts_through_the_librarys_grouped_product(name, monkeypatch):
     tu.check(got, name, streams, "bfloat16")
 
 
+@pytest.mark.parametrize("name", ["random1", "random2", "random3", "random5", "random8", "random13", "random21", "random34"])
+def test_configurations_drawn_at_random(name):
+    """Layer orders, sizes and constants that nobody chose (tomodra_util.random_config): whole prompts and a mixed
+    schedule through three slots, in float32 within its tolerance; bfloat16 must be finite and agree with the oracle in
+    the median (how far single rows lie depends on how a drawn model amplifies rounding)."""
+    folder = tu.model_folder(name)
+    streams = {f"{name}_{i}": tu.tokens_for(name, n, 80 + i) for i, n in enumerate((150, 3, 70, 1, 97))}
+    margin = min(tu.plain_run(name, toks)[1] for toks in streams.values())
+    whole = util.trace_whole(streams)
+    mixed = util.trace_mixed(streams, seed=5, live=3, tail=20)
+    got, _ = replay(name, "float32", whole, page_tokens=64)
+    tu.check(got, name, streams, "float32")
+    got, _ = replay(name, "float32", mixed, page_tokens=16, max_requests=3)
+    tu.check(got, name, streams, "float32")
+    for steps, page in ((whole, 16), (mixed, 64)):
+        got, _ = replay(name, "bfloat16", steps, page_tokens=page, max_requests=3)
+        means = []
+        for (rid, p), row in got.items():
+            ref = tu.plain_logits(name, streams[rid])[p]
+            assert np.isfinite(row).all()
+            means.append(np.abs(row - ref).mean() / max(1.0, np.abs(tu.plain_logits(name, streams[rid])).max()))
+        if margin > 0.01:
+            assert np.median(means) <= 2 * tu.BF16_MEDIAN_TOL, (name, float(np.median(means)))
+
+
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_float32_does_not_depend_on_the_cut_or_the_batch(name):
     streams = streams_for(name, 30, (97, 40, 131))
