@@ -279,6 +279,8 @@ grouped_gemm_tc_kernel(const GroupedArgs p) {
         if (step + GT_STAGES - 1 < steps) bring((step + GT_STAGES - 1) % GT_STAGES, (step + GT_STAGES - 1) * GT_BK);
         cp_async_commit();
         const __nv_bfloat16* As = staged + (size_t)(step % GT_STAGES) * (1 + NW) * TILE;
+        if (r0 >= rows) continue;                 // a warp whose 16 rows are all beyond the tile's (a step of few tokens
+                                                  // has one or two rows per expert) only helps to bring the weights
 #pragma unroll
         for (int kk = 0; kk < GT_BK; kk += 16) {
             uint32_t a0 = *reinterpret_cast<const uint32_t*>(As + (r0 + gq) * GT_LD + kk + 2 * tq);
